@@ -1,0 +1,116 @@
+// Python bindings (module teramoe_b200_C).  Thin: argument checks + raw-pointer calls into the
+// launchers declared in gemm.h / routing.h / comm.h / runtime.h.  No kernel code here.
+//
+// Reference counterpart: the pybind block at csrc/moe_extension.cpp:2573-2657.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "gemm.h"
+
+namespace {
+
+#define TM_CHECK_CUDA(call)                                                                          \
+    do {                                                                                             \
+        cudaError_t _e = (call);                                                                     \
+        TORCH_CHECK(_e == cudaSuccess, "teramoe_b200: ", #call, " failed: ", cudaGetErrorString(_e)); \
+    } while (0)
+
+void check_bf16(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bf16");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+void check_i32(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be a contiguous int32 CUDA tensor");
+}
+void check_f32(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(), name, " must be a contiguous fp32 CUDA tensor");
+}
+int* status_ptr(const c10::optional<torch::Tensor>& status) {
+    if (!status.has_value()) return nullptr;
+    check_i32(*status, "status");
+    TORCH_CHECK(status->numel() >= 4, "status must hold 4 ints");
+    return status->data_ptr<int>();
+}
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// ---- grouped GEMMs ------------------------------------------------------------------------------
+void gemm_fwd_gateup(torch::Tensor xperm, torch::Tensor w_gateup, torch::Tensor act, torch::Tensor preact, torch::Tensor row_w,
+                     torch::Tensor mblock_expert, torch::Tensor num_mblocks, c10::optional<torch::Tensor> status, int64_t num_sms) {
+    check_bf16(xperm, "xperm"); check_bf16(w_gateup, "w_gateup"); check_bf16(act, "act"); check_bf16(preact, "preact");
+    check_f32(row_w, "row_w"); check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    const int S = xperm.size(0), H = xperm.size(1), E = w_gateup.size(0), I = w_gateup.size(1) / 2;
+    TORCH_CHECK(S % 128 == 0 && w_gateup.size(2) == H && act.size(0) == S && act.size(1) == I && preact.size(0) == S &&
+                preact.size(1) == 2 * I && row_w.numel() == S && mblock_expert.numel() >= S / 128, "gemm_fwd_gateup: shape mismatch");
+    c10::cuda::CUDAGuard guard(xperm.device());
+    TM_CHECK_CUDA(tmoe::gemm_fwd_gateup(xperm.data_ptr(), w_gateup.data_ptr(), act.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(),
+                                        mblock_expert.data_ptr<int>(), num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status),
+                                        (int)num_sms, cur_stream()));
+}
+
+void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+                   c10::optional<torch::Tensor> status, int64_t num_sms) {
+    check_bf16(act, "act"); check_bf16(w_down, "w_down"); check_bf16(y, "y");
+    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    const int S = act.size(0), I = act.size(1), E = w_down.size(0), H = w_down.size(1);
+    TORCH_CHECK(S % 128 == 0 && w_down.size(2) == I && y.size(0) == S && y.size(1) == H && mblock_expert.numel() >= S / 128,
+                "gemm_fwd_down: shape mismatch");
+    c10::cuda::CUDAGuard guard(act.device());
+    TM_CHECK_CUDA(tmoe::gemm_fwd_down(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), mblock_expert.data_ptr<int>(),
+                                      num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+}
+
+void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor preact, torch::Tensor row_w, torch::Tensor dgu,
+                      torch::Tensor act_w, torch::Tensor droute_part, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+                      c10::optional<torch::Tensor> status, int64_t num_sms) {
+    check_bf16(dyperm, "dyperm"); check_bf16(w_down, "w_down"); check_bf16(preact, "preact"); check_bf16(dgu, "dgu"); check_bf16(act_w, "act_w");
+    check_f32(row_w, "row_w"); check_f32(droute_part, "droute_part");
+    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    const int S = dyperm.size(0), H = dyperm.size(1), E = w_down.size(0), I = w_down.size(2);
+    TORCH_CHECK(S % 128 == 0 && w_down.size(1) == H && preact.size(0) == S && preact.size(1) == 2 * I && dgu.size(0) == S &&
+                dgu.size(1) == 2 * I && act_w.size(0) == S && act_w.size(1) == I && row_w.numel() == S &&
+                droute_part.size(0) == S && droute_part.size(1) == tmoe::gemm_num_droute_parts(I) && mblock_expert.numel() >= S / 128,
+                "gemm_bwd_gradact: shape mismatch");
+    c10::cuda::CUDAGuard guard(dyperm.device());
+    TM_CHECK_CUDA(tmoe::gemm_bwd_gradact(dyperm.data_ptr(), w_down.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(), dgu.data_ptr(),
+                                         act_w.data_ptr(), droute_part.data_ptr<float>(), mblock_expert.data_ptr<int>(),
+                                         num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+}
+
+void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+                 c10::optional<torch::Tensor> status, int64_t num_sms) {
+    check_bf16(dgu, "dgu"); check_bf16(w_gateup, "w_gateup"); check_bf16(dxperm, "dxperm");
+    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    const int S = dgu.size(0), I = dgu.size(1) / 2, E = w_gateup.size(0), H = w_gateup.size(2);
+    TORCH_CHECK(S % 128 == 0 && w_gateup.size(1) == 2 * I && dxperm.size(0) == S && dxperm.size(1) == H && mblock_expert.numel() >= S / 128,
+                "gemm_bwd_dx: shape mismatch");
+    c10::cuda::CUDAGuard guard(dgu.device());
+    TM_CHECK_CUDA(tmoe::gemm_bwd_dx(dgu.data_ptr(), w_gateup.data_ptr(), dxperm.data_ptr(), mblock_expert.data_ptr<int>(),
+                                    num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+}
+
+void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tensor seg_offsets, c10::optional<torch::Tensor> status,
+                int64_t num_sms) {
+    check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(dw, "dw"); check_i32(seg_offsets, "seg_offsets");
+    const int S = a.size(0), M = a.size(1), N = b.size(1), E = dw.size(0);
+    TORCH_CHECK(b.size(0) == S && dw.size(1) == M && dw.size(2) == N && seg_offsets.numel() == E + 1, "gemm_wgrad: shape mismatch");
+    c10::cuda::CUDAGuard guard(dw.device());
+    TM_CHECK_CUDA(tmoe::gemm_wgrad(a.data_ptr(), b.data_ptr(), dw.data_ptr(), seg_offsets.data_ptr<int>(), S, M, N, E, status_ptr(status),
+                                   (int)num_sms, cur_stream()));
+}
+
+}  // namespace
+
+void register_more(pybind11::module_& m);  // routing / comm / runtime bindings (bindings_more.cpp)
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "teramoe_b200 native kernels (sm_100a)";
+    m.def("gemm_fwd_gateup", &gemm_fwd_gateup);
+    m.def("gemm_fwd_down", &gemm_fwd_down);
+    m.def("gemm_bwd_gradact", &gemm_bwd_gradact);
+    m.def("gemm_bwd_dx", &gemm_bwd_dx);
+    m.def("gemm_wgrad", &gemm_wgrad);
+    m.def("gemm_num_droute_parts", &tmoe::gemm_num_droute_parts);
+    register_more(m);
+}

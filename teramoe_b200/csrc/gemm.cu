@@ -1,0 +1,568 @@
+// Persistent, warp-specialised tcgen05 grouped GEMM family for the expert MLP.
+//
+// One kernel template covers the five contractions of a SwiGLU expert layer:
+//   forward   GU  = X . Wgu^T   (+ SwiGLU * route epilogue, pre-activation side store)
+//   forward   Y   = Act . Wd^T
+//   backward  gA  = dY . Wd     (B read MN-major straight from the forward layout; dSwiGLU epilogue)
+//   backward  dX  = dGU . Wgu   (B MN-major)
+//   backward  dW  = A^T . B     (both operands MN-major, K = the expert's rows, variable per expert)
+//
+// CTA layout (384 threads, one CTA per SM, 1-CTA UMMA 128x256x16):
+//   warp 0      TMA producer (one elected lane)        4-stage ring, 48 KB per stage
+//   warp 1      UMMA issuer  (one elected lane)        accumulators double-buffered in TMEM (2 x 256 cols)
+//   warp 2      tensor-memory allocation / release
+//   warp 3      idle
+//   warps 4-11  epilogue: warp w reads TMEM lanes 32*(w%4).. and column half (w-4)/4
+//
+// All waits are bounded (ptx.cuh).  Tiles never straddle experts because every expert's segment in
+// slot space is padded to a multiple of 128 rows.
+//
+// Reference counterpart: csrc/teramoe/teramoe_wrapper.cuh:46-98 (tile config), :530-780 (mainloop),
+// csrc/teramoe/teramoe_sm100_bf16_compute.cuh:567-746 (SwiGLU epilogue).  Written from the PTX ISA
+// description of tcgen05 / TMA, not from that code: different tile (128x256 vs 128x128), 8 epilogue
+// warps, dSwiGLU and route-gradient fused in the epilogue, varlen-K weight-gradient mode.
+#include "gemm.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "ptx.cuh"
+
+namespace tmoe {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UK = 16;
+constexpr int kStages = 4;
+constexpr int kAStageBytes = BM * BK * 2;  // 16 KB
+constexpr int kBStageBytes = BN * BK * 2;  // 32 KB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kAtomBytes = 64 * BK * 2;  // one 64(MN) x 64(K) MN-major swizzle atom column: 8 KB
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 128 + 32 * kEpiWarps;
+constexpr int kTmemCols = 512;
+constexpr int kSuperM = 16;  // m-blocks per L2 super-group
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int { kEpiStore = 0, kEpiSwiGLU = 1, kEpiDSwiGLU = 2 };
+
+struct GemmArgs {
+    int n_total;                 // columns of D per group
+    int k_total;                 // K of the M-grouped modes
+    int num_n_blocks;            // ceil(n_total / BN)
+    int max_mblocks;             // static bound on m-blocks (M-grouped) or ceil(m_total / BM) (K-grouped)
+    const int* num_mblocks_dev;  // optional device-side live count (M-grouped)
+    const int* mblock_expert;    // [max_mblocks] expert of each m-block (M-grouped)
+    int b_group_rows;            // rows of the B tensor map per expert
+    int num_groups;              // K-grouped: number of experts
+    const int* seg_offsets;      // K-grouped: [num_groups + 1] row offsets, multiples of 128
+    int m_total;                 // K-grouped: rows of dW per expert
+    __nv_bfloat16* d;            // main output
+    int ldd;
+    __nv_bfloat16* aux;          // preact (fwd gate_up) / dGU (bwd grad_act)
+    int ld_aux;
+    const __nv_bfloat16* preact; // bwd grad_act input
+    const float* row_w;          // route weight per slot row
+    float* droute_part;          // bwd grad_act: [rows, n_parts]
+    int n_parts;
+    int* status;
+};
+
+struct Tile {
+    int m_blk, n_blk, group, k0, nk;  // k0: first K row (elements), nk: number of BK blocks
+};
+
+template <bool KGROUP>
+__device__ __forceinline__ bool get_tile(const GemmArgs& g, int t, int num_mblocks, Tile& tile) {
+    if constexpr (!KGROUP) {
+        const int total = num_mblocks * g.num_n_blocks;
+        if (t >= total) return false;
+        const int per_super = kSuperM * g.num_n_blocks;
+        const int super = t / per_super;
+        const int r = t - super * per_super;
+        const int m_first = super * kSuperM;
+        const int m_cnt = min(kSuperM, num_mblocks - m_first);
+        tile.n_blk = r / m_cnt;
+        tile.m_blk = m_first + (r - tile.n_blk * m_cnt);
+        tile.group = g.mblock_expert[tile.m_blk];
+        tile.k0 = 0;
+        tile.nk = g.k_total / BK;
+        return true;
+    } else {
+        const int per_group = g.max_mblocks * g.num_n_blocks;
+        const int total = g.num_groups * per_group;
+        if (t >= total) return false;
+        tile.group = t / per_group;
+        const int r = t - tile.group * per_group;
+        tile.n_blk = r / g.max_mblocks;
+        tile.m_blk = r - tile.n_blk * g.max_mblocks;
+        const int s0 = g.seg_offsets[tile.group];
+        const int s1 = g.seg_offsets[tile.group + 1];
+        tile.k0 = s0;
+        tile.nk = (s1 - s0) / BK;
+        return true;
+    }
+}
+
+__device__ __forceinline__ void store_bf16x8(__nv_bfloat16* p, const uint32_t* acc) {
+    int4 v;
+    v.x = (int)pack_bf16x2(__uint_as_float(acc[0]), __uint_as_float(acc[1]));
+    v.y = (int)pack_bf16x2(__uint_as_float(acc[2]), __uint_as_float(acc[3]));
+    v.z = (int)pack_bf16x2(__uint_as_float(acc[4]), __uint_as_float(acc[5]));
+    v.w = (int)pack_bf16x2(__uint_as_float(acc[6]), __uint_as_float(acc[7]));
+    *reinterpret_cast<int4*>(p) = v;
+}
+
+template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle needs 1024-byte aligned stage bases.
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kStages * kStageBytes;
+    // barrier words (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+    auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull_bar(s), 1);
+            mbar_init(tempty_bar(s), kEpiWarps);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 2) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int num_mblocks = g.max_mblocks;
+    if constexpr (!KGROUP) {
+        if (g.num_mblocks_dev != nullptr) num_mblocks = min(*g.num_mblocks_dev, g.max_mblocks);
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t issued = 0;
+            bool ok = true;
+            Tile tile;
+            for (int t = blockIdx.x; ok && get_tile<KGROUP>(g, t, num_mblocks, tile); t += gridDim.x) {
+                const int m0 = tile.m_blk * BM;
+                const int n0 = tile.n_blk * BN;
+                for (int kb = 0; kb < tile.nk; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, 100)) { ok = false; break; }
+                    const uint32_t a_dst = smem_base + stage * kStageBytes;
+                    const uint32_t b_dst = a_dst + kAStageBytes;
+                    const uint32_t bar = full_bar(stage);
+                    mbar_arrive_expect_tx(bar, kStageBytes);
+                    const int k = tile.k0 + kb * BK;
+                    if constexpr (!A_MN) {
+                        tma_load_2d(a_dst, &map_a, bar, k, m0);  // box {64 K, 128 rows}
+                    } else {
+#pragma unroll
+                        for (int a = 0; a < BM / 64; ++a) tma_load_2d(a_dst + a * kAtomBytes, &map_a, bar, m0 + 64 * a, k);
+                    }
+                    if constexpr (!B_MN) {
+                        tma_load_2d(b_dst, &map_b, bar, k, tile.group * g.b_group_rows + n0);  // box {64 K, 256 rows}
+                    } else {
+                        const int krow = KGROUP ? k : tile.group * g.b_group_rows + k;
+#pragma unroll
+                        for (int a = 0; a < BN / 64; ++a) tma_load_2d(b_dst + a * kAtomBytes, &map_b, bar, n0 + 64 * a, krow);
+                    }
+                    ++issued;
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Gave up: let copies that are still in flight land before the CTA's shared memory is released.
+                const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
+                for (uint32_t i = 0; i < pending; ++i) {
+                    const int s = (stage + kStages - 1 - (int)i) % kStages;
+                    const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ UMMA issuer
+        constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        Tile tile;
+        int iter = 0;
+        for (int t = blockIdx.x; ok && get_tile<KGROUP>(g, t, num_mblocks, tile); t += gridDim.x, ++iter) {
+            const int as = iter & 1;
+            const uint32_t aphase = (iter >> 1) & 1;
+            if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, 200)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+            for (int kb = 0; kb < tile.nk; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag, g.status, 201)) { ok = false; break; }
+                tcgen05_fence_after();
+                if (elect_one()) {
+                    const uint32_t a_addr = smem_base + stage * kStageBytes;
+                    const uint32_t b_addr = a_addr + kAStageBytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UK; ++k) {
+                        // K-major: 32 bytes per UMMA_K inside the 128-byte swizzle row; 8-row groups 1024 B apart.
+                        // MN-major: 16 K-rows of 128 B per UMMA_K; 64-wide MN atoms BK*128 B apart.
+                        const uint64_t a_desc = A_MN ? make_smem_desc_sw128(a_addr + k * (UK * 128), kAtomBytes, 1024)
+                                                     : make_smem_desc_sw128(a_addr + k * (UK * 2), 0, 1024);
+                        const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_addr + k * (UK * 128), kAtomBytes, 1024)
+                                                     : make_smem_desc_sw128(b_addr + k * (UK * 2), 0, 1024);
+                        umma_bf16_ss(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));
+                    if (kb == tile.nk - 1) umma_commit(tfull_bar(as));
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok && tile.nk == 0) {
+                if (elect_one()) umma_commit(tfull_bar(as));  // nothing to accumulate: epilogue writes zeros
+                __syncwarp();
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3;          // TMEM lane quarter
+        const int h = (warp - 4) >> 2;   // column half of the accumulator
+        const int r = q * 32 + lane;     // row inside the tile
+        bool ok = true;
+        Tile tile;
+        int iter = 0;
+        for (int t = blockIdx.x; ok && get_tile<KGROUP>(g, t, num_mblocks, tile); t += gridDim.x, ++iter) {
+            const int as = iter & 1;
+            const uint32_t aphase = (iter >> 1) & 1;
+            if (!mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, 300)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN + h * (BN / 2));
+            const int n0 = tile.n_blk * BN + h * (BN / 2);  // first accumulator column handled by this thread
+            const bool zero_tile = (tile.nk == 0);
+            long row;
+            bool row_ok = true;
+            if constexpr (!KGROUP) {
+                row = (long)tile.m_blk * BM + r;
+            } else {
+                row_ok = (tile.m_blk * BM + r) < g.m_total;
+                row = (long)tile.group * g.m_total + tile.m_blk * BM + r;
+            }
+            float w = 0.f;
+            if constexpr (EPI != kEpiStore) w = g.row_w[row];
+            float droute = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < (BN / 2) / 32; ++c) {
+                uint32_t acc[32];
+                tmem_ld_x32(taddr0 + (uint32_t)(c * 32), acc);
+                tmem_ld_wait();
+                const int col = n0 + c * 32;
+                if (zero_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = 0u;
+                }
+                if constexpr (EPI == kEpiStore) {
+                    if (row_ok) {
+                        __nv_bfloat16* dst = g.d + row * g.ldd + col;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            if (col + v * 8 + 8 <= g.n_total) store_bf16x8(dst + v * 8, acc + v * 8);
+                    }
+                } else if constexpr (EPI == kEpiSwiGLU) {
+                    // accumulator columns (2j, 2j+1) = (gate_j, up_j); n_total = 2I
+                    if (col < g.n_total) {
+                        store_bf16x8(g.aux + row * g.ld_aux + col, acc);
+                        store_bf16x8(g.aux + row * g.ld_aux + col + 8, acc + 8);
+                        store_bf16x8(g.aux + row * g.ld_aux + col + 16, acc + 16);
+                        store_bf16x8(g.aux + row * g.ld_aux + col + 24, acc + 24);
+                        uint32_t o[8];
+#pragma unroll
+                        for (int p = 0; p < 8; ++p) {
+                            float a2[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const float gt = __uint_as_float(acc[4 * p + 2 * e]);
+                                const float up = __uint_as_float(acc[4 * p + 2 * e + 1]);
+                                a2[e] = gt / (1.f + expf(-gt)) * up * w;
+                            }
+                            o[p] = pack_bf16x2(a2[0], a2[1]);
+                        }
+                        __nv_bfloat16* dst = g.d + row * g.ldd + (col >> 1);
+                        *reinterpret_cast<int4*>(dst) = make_int4((int)o[0], (int)o[1], (int)o[2], (int)o[3]);
+                        *reinterpret_cast<int4*>(dst + 8) = make_int4((int)o[4], (int)o[5], (int)o[6], (int)o[7]);
+                    }
+                } else {
+                    // accumulator column j = d act_j; n_total = I.  preact holds (g_j, u_j) at [2j, 2j+1].
+                    if (col < g.n_total) {
+                        const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
+                        uint32_t dgu[32];
+                        uint32_t aw[16];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const int4 pv = pp[v];
+                            const uint32_t pr[4] = {(uint32_t)pv.x, (uint32_t)pv.y, (uint32_t)pv.z, (uint32_t)pv.w};
+                            float av[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 gu = unpack_bf16x2(pr[e]);
+                                const float ga = __uint_as_float(acc[4 * v + e]);
+                                const float sig = 1.f / (1.f + __expf(-gu.x));
+                                const float s = gu.x * sig;
+                                const float a = s * gu.y;
+                                const float gaw = ga * w;
+                                const float d_up = s * gaw;
+                                const float d_gate = (sig - s * sig + s) * gaw * gu.y;
+                                dgu[4 * v + e] = pack_bf16x2(d_gate, d_up);
+                                av[e] = a * w;
+                                droute += ga * a;
+                            }
+                            aw[2 * v] = pack_bf16x2(av[0], av[1]);
+                            aw[2 * v + 1] = pack_bf16x2(av[2], av[3]);
+                        }
+                        int4* dg = reinterpret_cast<int4*>(g.aux + row * g.ld_aux + 2 * col);
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            dg[v] = make_int4((int)dgu[4 * v], (int)dgu[4 * v + 1], (int)dgu[4 * v + 2], (int)dgu[4 * v + 3]);
+                        int4* da = reinterpret_cast<int4*>(g.d + row * g.ldd + col);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            da[v] = make_int4((int)aw[4 * v], (int)aw[4 * v + 1], (int)aw[4 * v + 2], (int)aw[4 * v + 3]);
+                    }
+                }
+            }
+            if constexpr (EPI == kEpiDSwiGLU) g.droute_part[row * g.n_parts + tile.n_blk * 2 + h] = droute;
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(as));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D bf16 row-major tensor [rows, cols] (cols contiguous), box {box_cols, box_rows}, 128-byte swizzle.
+cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return cudaErrorInvalidValue;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
+cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms,
+                   cudaStream_t stream) {
+    auto kern = grouped_gemm_kernel<A_MN, B_MN, KGROUP, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    if (total_tiles <= 0) return cudaSuccess;
+    int grid = total_tiles < num_sms ? total_tiles : num_sms;
+    kern<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, g);
+    return cudaGetLastError();
+}
+
+int default_sms(int num_sms) {
+    if (num_sms > 0) return num_sms;
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return cached;
+}
+
+}  // namespace
+
+int gemm_num_droute_parts(int I) { return 2 * ((I + BN - 1) / BN); }
+
+cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, void* preact, const float* row_w,
+                            const int* mblock_expert, const int* num_mblocks_dev, int max_mblocks, int H, int I,
+                            int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+    if (max_mblocks <= 0) return cudaSuccess;
+    if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, xperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    if ((e = make_map(&mb, w_gateup, (uint64_t)num_local_experts * 2 * I, H, BK, BN)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.n_total = 2 * I;
+    g.k_total = H;
+    g.num_n_blocks = (2 * I + BN - 1) / BN;
+    g.max_mblocks = max_mblocks;
+    g.num_mblocks_dev = num_mblocks_dev;
+    g.mblock_expert = mblock_expert;
+    g.b_group_rows = 2 * I;
+    g.d = static_cast<__nv_bfloat16*>(act);
+    g.ldd = I;
+    g.aux = static_cast<__nv_bfloat16*>(preact);
+    g.ld_aux = 2 * I;
+    g.row_w = row_w;
+    g.status = status;
+    return launch<false, false, false, kEpiSwiGLU>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+}
+
+cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const int* mblock_expert,
+                          const int* num_mblocks_dev, int max_mblocks, int H, int I, int num_local_experts, int* status,
+                          int num_sms, cudaStream_t stream) {
+    if (max_mblocks <= 0) return cudaSuccess;
+    if (I % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, act, (uint64_t)max_mblocks * BM, I, BK, BM)) != cudaSuccess) return e;
+    if ((e = make_map(&mb, w_down, (uint64_t)num_local_experts * H, I, BK, BN)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.n_total = H;
+    g.k_total = I;
+    g.num_n_blocks = (H + BN - 1) / BN;
+    g.max_mblocks = max_mblocks;
+    g.num_mblocks_dev = num_mblocks_dev;
+    g.mblock_expert = mblock_expert;
+    g.b_group_rows = H;
+    g.d = static_cast<__nv_bfloat16*>(y);
+    g.ldd = H;
+    g.status = status;
+    return launch<false, false, false, kEpiStore>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+}
+
+cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void* preact, const float* row_w, void* dgu,
+                             void* act_w, float* droute_part, const int* mblock_expert, const int* num_mblocks_dev,
+                             int max_mblocks, int H, int I, int num_local_experts, int* status, int num_sms,
+                             cudaStream_t stream) {
+    if (max_mblocks <= 0) return cudaSuccess;
+    if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, dyperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    // W_down [E*H, I]: K = H rows, N = I contiguous -> MN-major B, box {64 N, 64 K}
+    if ((e = make_map(&mb, w_down, (uint64_t)num_local_experts * H, I, 64, BK)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.n_total = I;
+    g.k_total = H;
+    g.num_n_blocks = (I + BN - 1) / BN;
+    g.max_mblocks = max_mblocks;
+    g.num_mblocks_dev = num_mblocks_dev;
+    g.mblock_expert = mblock_expert;
+    g.b_group_rows = H;
+    g.d = static_cast<__nv_bfloat16*>(act_w);
+    g.ldd = I;
+    g.aux = static_cast<__nv_bfloat16*>(dgu);
+    g.ld_aux = 2 * I;
+    g.preact = static_cast<const __nv_bfloat16*>(preact);
+    g.row_w = row_w;
+    g.droute_part = droute_part;
+    g.n_parts = gemm_num_droute_parts(I);
+    g.status = status;
+    return launch<false, true, false, kEpiDSwiGLU>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+}
+
+cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const int* mblock_expert,
+                        const int* num_mblocks_dev, int max_mblocks, int H, int I, int num_local_experts, int* status,
+                        int num_sms, cudaStream_t stream) {
+    if (max_mblocks <= 0) return cudaSuccess;
+    if ((2 * I) % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, dgu, (uint64_t)max_mblocks * BM, 2 * I, BK, BM)) != cudaSuccess) return e;
+    // W_gateup [E*2I, H]: K = 2I rows, N = H contiguous -> MN-major B
+    if ((e = make_map(&mb, w_gateup, (uint64_t)num_local_experts * 2 * I, H, 64, BK)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.n_total = H;
+    g.k_total = 2 * I;
+    g.num_n_blocks = (H + BN - 1) / BN;
+    g.max_mblocks = max_mblocks;
+    g.num_mblocks_dev = num_mblocks_dev;
+    g.mblock_expert = mblock_expert;
+    g.b_group_rows = 2 * I;
+    g.d = static_cast<__nv_bfloat16*>(dxperm);
+    g.ldd = H;
+    g.status = status;
+    return launch<false, true, false, kEpiStore>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+}
+
+cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_offsets, int total_rows, int M, int N,
+                       int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+    if (num_local_experts <= 0) return cudaSuccess;
+    if (M % 8 != 0 || N % 8 != 0) return cudaErrorInvalidValue;
+    // The tensor maps must cover at least one row so that encoding succeeds when nothing was received.
+    const uint64_t rows = total_rows > 0 ? (uint64_t)total_rows : 1;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, a, rows, M, 64, BK)) != cudaSuccess) return e;
+    if ((e = make_map(&mb, b, rows, N, 64, BK)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.n_total = N;
+    g.num_n_blocks = (N + BN - 1) / BN;
+    g.max_mblocks = (M + BM - 1) / BM;
+    g.num_groups = num_local_experts;
+    g.seg_offsets = seg_offsets;
+    g.m_total = M;
+    g.d = static_cast<__nv_bfloat16*>(dw);
+    g.ldd = N;
+    g.status = status;
+    return launch<true, true, true, kEpiStore>(ma, mb, g, num_local_experts * g.max_mblocks * g.num_n_blocks,
+                                               default_sms(num_sms), stream);
+}
+
+}  // namespace tmoe
