@@ -1,0 +1,369 @@
+"""`Buffer`: the public entry point, signature-compatible with the reference's `teramoe.Buffer`.
+
+Reference counterparts: teramoe/buffer.py:32-147 (construction / destroy), :153-290 (knobs, configs),
+:293-454 (layout, dispatch, combine), :537-708 (low-latency API), :710-818 (fused autograd entry
+points).  Differences that matter to callers:
+
+* One NVSwitch node only (EP = 1, 2, 4, 8): `num_rdma_bytes`, `num_qps_per_rank`, `allow_mnnvl`,
+  `use_fabric` are accepted and ignored; the documented constructor call works on <= 8 ranks (the
+  reference rejects it there, csrc/moe_extension.cpp:161-162).
+* `num_nvl_bytes` is a starting size: the symmetric arena grows (collectively) when a call needs more.
+* Slot assignment is deterministic, so results are bitwise reproducible run to run.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple, Union
+
+import torch
+import torch.distributed as dist
+
+from .config import Config, topk_idx_t
+from .engine import EPEngine, LayerHandle
+from .parallel.world import EPWorld
+from .utils.events import EventHandle, EventOverlap
+from .utils.nvlink import check_nvlink_connections
+
+
+class _TeraMoEFunction(torch.autograd.Function):
+    """Autograd wrapper of the layer: gradients for x, topk_weights, W_gateup and W_down."""
+
+    @staticmethod
+    def forward(ctx, buffer, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, grad_topk_weights, opts):
+        needs_bwd = any(t.requires_grad for t in (x, topk_weights, W_gateup, W_down))
+        out, saved = buffer._drive(buffer._engine.forward_gen(x, topk_idx, topk_weights, W_gateup, W_down, num_experts,
+                                                              keep_for_backward=needs_bwd, impl=opts))
+        ctx.buffer = buffer
+        ctx.saved = saved
+        ctx.grad_topk_weights = grad_topk_weights
+        ctx.opts = opts
+        ctx.save_for_backward(W_gateup, W_down)          # x itself is not kept (teramoe/buffer.py:726-727)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_out):
+        W_gateup, W_down = ctx.saved_tensors
+        buffer = ctx.buffer
+        dx, gtw, dWgu, dWd = buffer._drive(buffer._engine.backward_gen(ctx.saved, grad_out.contiguous(), W_gateup, W_down,
+                                                                      impl=ctx.opts))
+        ctx.saved = None
+        if ctx.grad_topk_weights is not None:
+            ctx.grad_topk_weights.copy_(gtw)
+            gtw = ctx.grad_topk_weights
+        return None, dx, None, gtw, dWgu, dWd, None, None, None
+
+
+class Buffer:
+    """Expert-parallel communication + fused MoE layer on one NVSwitch node."""
+
+    num_sms: int = 20
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, num_nvl_bytes: int = 0, num_rdma_bytes: int = 0,
+                 low_latency_mode: bool = False, num_qps_per_rank: int = 24, allow_nvlink_for_low_latency_mode: bool = True,
+                 allow_mnnvl: bool = False, use_fabric: bool = False, explicitly_destroy: bool = False, enable_shrink: bool = False,
+                 comm=None, device: Optional[Union[str, torch.device]] = None) -> None:
+        if num_nvl_bytes % 128 != 0 or num_rdma_bytes % 128 != 0:
+            raise ValueError("buffer sizes must be multiples of 128 bytes")
+        if comm is not None and group is None:
+            raise NotImplementedError("mpi4py bootstrap is not available; pass a torch.distributed group")
+        if group is None and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            group = dist.group.WORLD
+        if device is None:
+            use_cuda = torch.cuda.is_available() and (group is None or dist.get_backend(group) != "gloo")
+            device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+        self.device = torch.device(device)
+        self.group = group
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.group_size = dist.get_world_size(group) if group is not None else 1
+        if self.group_size > 8:
+            raise ValueError("teramoe_b200 runs on one NVSwitch node: at most 8 ranks")
+        self.num_nvl_bytes, self.num_rdma_bytes = num_nvl_bytes, num_rdma_bytes
+        self.low_latency_mode = low_latency_mode
+        self.explicitly_destroy = explicitly_destroy
+        self.enable_shrink = enable_shrink
+        self._destroyed = False
+        if group is not None and self.device.type == "cuda":
+            check_nvlink_connections(group)
+        self._world = EPWorld.from_group(group, self.device) if group is not None else EPWorld.single(self.device)
+        self._engine = EPEngine(self._world)
+        self._comm_stream = torch.cuda.Stream(self.device, priority=-1) if self.device.type == "cuda" else None
+        if self.device.type == "cuda" and num_nvl_bytes > 0:
+            self._world.ensure_data(num_nvl_bytes)
+        self._ll_masked = set()
+        self._ll_next_buffer = 0
+
+    # ------------------------------------------------------------------ lifecycle
+    def destroy(self) -> None:
+        """Release the symmetric arenas (collective).  Requires explicitly_destroy=True, like the reference."""
+        if not self.explicitly_destroy:
+            raise RuntimeError("`explicitly_destroy` flag must be set to call destroy()")
+        self._destroy()
+
+    def _destroy(self) -> None:
+        if not self._destroyed:
+            self._destroyed = True
+            self._world.close()
+
+    def __del__(self):
+        try:
+            if not self._destroyed and not self.explicitly_destroy:
+                self._destroy()
+        except Exception:
+            pass
+
+    def _drive(self, gen):
+        if self._destroyed:
+            raise RuntimeError("Buffer was destroyed")
+        return self._world.drive(gen)
+
+    def state(self) -> dict:
+        """Sizes and configuration needed to rebuild an equivalent Buffer (nothing else persists between calls)."""
+        return {"rank": self.rank, "group_size": self.group_size, "device": str(self.device), "num_nvl_bytes": self.num_nvl_bytes,
+                "arena_bytes": self._world.data_bytes, "num_sms": Buffer.num_sms, "low_latency_mode": self.low_latency_mode}
+
+    # ------------------------------------------------------------------ knobs
+    @staticmethod
+    def is_sm90_compiled() -> bool:
+        return False
+
+    @staticmethod
+    def set_num_sms(new_num_sms: int) -> None:
+        if new_num_sms % 2 != 0:
+            raise ValueError("The SM count must be even")
+        Buffer.num_sms = new_num_sms
+
+    @staticmethod
+    def capture() -> EventOverlap:
+        return EventOverlap(EventHandle())
+
+    @staticmethod
+    def get_low_latency_rdma_size_hint(num_max_dispatch_tokens_per_rank: int, hidden: int, num_ranks: int, num_experts: int) -> int:
+        """Bytes of symmetric memory used by the low-latency layout (two buffers of per-expert,
+        per-source windows, bf16 payload + 16-byte header), cf. csrc/config.hpp:133-219."""
+        per_msg = 16 + hidden * 2
+        one = num_experts * num_max_dispatch_tokens_per_rank * per_msg
+        return ((2 * 2 * one + num_experts * 8) + 127) // 128 * 128
+
+    def get_comm_stream(self):
+        return self._comm_stream
+
+    def get_local_buffer_tensor(self, dtype: torch.dtype, size: Optional[torch.Size] = None, offset: int = 0,
+                                use_rdma_buffer: bool = False) -> torch.Tensor:
+        if self.device.type != "cuda" or self._world.data is None:
+            raise RuntimeError("no symmetric arena allocated yet")
+        elem = torch.empty((), dtype=dtype).element_size()
+        n = (self._world.data_bytes - offset) // elem
+        t = self._world.data.view(offset, [n], dtype)
+        return t if size is None else t[: int(torch.Size(size).numel())].view(size)
+
+    @staticmethod
+    def get_dispatch_config(num_ranks: int) -> Config:
+        if num_ranks not in (1, 2, 4, 8):
+            raise ValueError(f"unsupported number of EP ranks: {num_ranks}")
+        return Config(Buffer.num_sms, 24 if num_ranks <= 2 else 6, 256, 6, 128)
+
+    @staticmethod
+    def get_combine_config(num_ranks: int) -> Config:
+        if num_ranks not in (1, 2, 4, 8):
+            raise ValueError(f"unsupported number of EP ranks: {num_ranks}")
+        return Config(Buffer.num_sms, 10 if num_ranks <= 2 else 4, 256, 6, 128)
+
+    # ------------------------------------------------------------------ stream protocol helpers
+    def _enter(self, previous_event, allocate_on_comm_stream):
+        if self._comm_stream is None:
+            return None
+        cur = torch.cuda.current_stream(self.device)
+        if previous_event is not None and previous_event.event is not None and previous_event.event.event is not None:
+            self._comm_stream.wait_event(previous_event.event.event)
+        else:
+            self._comm_stream.wait_stream(cur)
+        return cur
+
+    def _leave(self, cur, async_finish, tensors) -> EventOverlap:
+        if self._comm_stream is None:
+            return EventOverlap(None)
+        if async_finish:
+            ev = EventHandle(self._comm_stream)
+            for t in tensors:
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    t.record_stream(self._comm_stream)
+                    t.record_stream(cur)
+            return EventOverlap(ev, tuple(t for t in tensors if isinstance(t, torch.Tensor)))
+        cur.wait_stream(self._comm_stream)
+        return EventOverlap(None)
+
+    def _on_comm_stream(self, fn: Callable, previous_event, async_finish, allocate_on_comm_stream):
+        if self._comm_stream is None:
+            return fn(), EventOverlap(None)
+        cur = self._enter(previous_event, allocate_on_comm_stream)
+        with torch.cuda.stream(self._comm_stream):
+            res = fn()
+        flat = res if isinstance(res, (tuple, list)) else (res,)
+        return res, self._leave(cur, async_finish, flat)
+
+    # ------------------------------------------------------------------ layout / dispatch / combine
+    def get_dispatch_layout(self, topk_idx: torch.Tensor, num_experts: int, previous_event: Optional[EventOverlap] = None,
+                            async_finish: bool = False, allocate_on_comm_stream: bool = False):
+        """-> (num_tokens_per_rank [ranks] i32, None, num_tokens_per_expert [E] i32, is_token_in_rank [T,ranks] bool, event)."""
+        N = self.group_size
+
+        def run():
+            T, K = topk_idx.shape
+            El = num_experts // N
+            if topk_idx.is_cuda:
+                ext = self._world.ext
+                C = num_experts + N + 2
+                chunk = ext.route_chunk_tokens()
+                chunks = max(1, (T + chunk - 1) // chunk)
+                hist = torch.zeros(chunks * C, dtype=torch.int32, device=topk_idx.device)
+                if T > 0:
+                    ext.route_hist(topk_idx.contiguous(), num_experts, N, hist)
+                tot = hist.view(chunks, C).sum(0, dtype=torch.int32)
+                per_expert, per_rank = tot[:num_experts].contiguous(), tot[num_experts:num_experts + N].contiguous()
+                valid = (topk_idx >= 0) & (topk_idx < num_experts)
+                d = torch.where(valid, topk_idx // El, torch.zeros_like(topk_idx)).long()
+                in_rank = torch.zeros(T, N, dtype=torch.int32, device=topk_idx.device).scatter_reduce_(1, d, valid.int(), reduce="amax").bool()
+            else:
+                from . import layout as L
+                row = L.count_row(topk_idx, num_experts, N)
+                per_expert, per_rank = row[:num_experts].contiguous(), row[num_experts:num_experts + N].contiguous()
+                in_rank = L.token_rank_hits(topk_idx, num_experts, N)
+            return per_rank, None, per_expert, in_rank
+
+        res, ev = self._on_comm_stream(run, previous_event, async_finish, allocate_on_comm_stream)
+        return (*res, ev)
+
+    def deepep_dispatch(self, x, handle: Optional[LayerHandle] = None, num_tokens_per_rank=None, num_tokens_per_rdma_rank=None,
+                        is_token_in_rank=None, num_tokens_per_expert=None, topk_idx: Optional[torch.Tensor] = None,
+                        topk_weights: Optional[torch.Tensor] = None, expert_alignment: int = 1, num_worst_tokens: int = 0,
+                        config: Optional[Config] = None, previous_event: Optional[EventOverlap] = None, async_finish: bool = False,
+                        allocate_on_comm_stream: bool = False, num_experts: Optional[int] = None):
+        """Un-fused dispatch.  -> (recv_x, recv_topk_idx, recv_topk_weights, num_recv_tokens_per_expert_list, handle, event).
+
+        Rows arrive once per (token, rank), ordered by source rank then token.  `recv_topk_idx` holds
+        LOCAL expert ids (-1 for experts of other ranks, weights zeroed there), like
+        csrc/kernels/intranode.cu:369-378.  With `handle=` (cached mode) only the payload moves and
+        no host synchronisation happens."""
+        if isinstance(x, tuple):
+            raise NotImplementedError("FP8 (x, scales) payloads are not supported by the bf16 training path")
+        x = x.contiguous()
+
+        def run():
+            eng = self._engine
+            if handle is not None:
+                h = handle
+                tabs, _ = self._drive(eng.dispatch_gen(h, x, None, with_meta=False))
+                return tabs["recv_x"][: h.rows].clone(), None, None, None, h
+            if topk_idx is None or topk_weights is None:
+                raise ValueError("topk_idx and topk_weights are required without a cached handle")
+            E = num_experts if num_experts is not None else (int(num_tokens_per_expert.numel()) if num_tokens_per_expert is not None else None)
+            if E is None:
+                raise ValueError("pass num_tokens_per_expert (from get_dispatch_layout) or num_experts")
+            h = self._drive(eng.layout_gen(topk_idx.contiguous(), E))
+            h.topk_weights = topk_weights
+            tabs, _ = self._drive(eng.dispatch_gen(h, x, topk_weights.float().contiguous(), with_meta=True))
+            eng.snapshot_tables(h, tabs)
+            recv_x = tabs["recv_x"][: h.rows].clone()
+            R, K = h.rows, h.K
+            rs = h.row_slots.long()
+            valid = rs >= 0
+            sl = rs.clamp(min=0)
+            kpos = (h.slot_tk.long()[sl] % K)
+            recv_idx = torch.full((R, K), -1, dtype=topk_idx.dtype, device=x.device)
+            recv_w = torch.zeros(R, K, dtype=torch.float32, device=x.device)
+            rr = torch.arange(R, device=x.device).view(R, 1).expand(R, K)
+            le = h.mblock_expert.long()[sl // 128] if h.slots > 0 else sl
+            recv_idx[rr[valid], kpos[valid]] = le[valid].to(topk_idx.dtype)
+            recv_w[rr[valid], kpos[valid]] = h.slot_w[sl[valid]]
+            counts = h.expert_total_local.tolist()
+            counts = [(c + expert_alignment - 1) // expert_alignment * expert_alignment for c in counts]
+            return recv_x, recv_idx, recv_w, counts, h
+
+        res, ev = self._on_comm_stream(run, previous_event, async_finish, allocate_on_comm_stream)
+        return (*res, ev)
+
+    def deepep_combine(self, x: torch.Tensor, handle: LayerHandle, topk_weights: Optional[torch.Tensor] = None, bias=None,
+                       config: Optional[Config] = None, previous_event: Optional[EventOverlap] = None, async_finish: bool = False,
+                       allocate_on_comm_stream: bool = False):
+        """Un-fused combine: un-weighted sum over ranks of the rows given for each token (+ up to two
+        bias tensors).  -> (combined_x [T,H], combined_topk_weights [T,K] or None, event)."""
+        h = handle
+
+        def run():
+            out, cw = self._drive(self._engine.combine_rows_gen(h, x, topk_weights))
+            if bias is not None:
+                for b in (bias if isinstance(bias, (tuple, list)) else (bias,)):
+                    if b is not None:
+                        out = (out.float() + b.float()).to(out.dtype)
+            return out, cw
+
+        res, ev = self._on_comm_stream(run, previous_event, async_finish, allocate_on_comm_stream)
+        return (*res, ev)
+
+    # reference aliases (teramoe/buffer.py:453-454)
+    dispatch = deepep_dispatch
+    combine = deepep_combine
+
+    def internode_dispatch(self, *args, **kwargs):
+        """There is no second (RDMA) tier on one NVSwitch node: same as deepep_dispatch."""
+        return self.deepep_dispatch(*args, **kwargs)
+
+    def internode_combine(self, *args, **kwargs):
+        return self.deepep_combine(*args, **kwargs)
+
+    # ------------------------------------------------------------------ fused layer
+    def _check_layer_args(self, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms, num_combine_sms,
+                          total_sms, stage, compute_batch_size, combine_start_head_percent):
+        if x.is_cuda and x.dtype != torch.bfloat16:
+            raise ValueError("teramoe_autograd only supports bf16 inputs on CUDA")
+        if x.dim() != 2 or topk_idx.dim() != 2 or topk_weights.shape != topk_idx.shape or topk_idx.shape[0] != x.shape[0]:
+            raise ValueError("expected x [T,H], topk_idx [T,K], topk_weights [T,K]")
+        if topk_idx.dtype not in (torch.int64, torch.int32):
+            raise ValueError("topk_idx must be int64 or int32")
+        if topk_idx.shape[1] > 32:
+            raise ValueError("top-k must be <= 32")
+        if num_dispatch_sms % 2 or num_combine_sms % 2:
+            raise ValueError("num_dispatch_sms and num_combine_sms must be even")
+        if stage not in (1, 2):
+            raise ValueError("stage must be 1 or 2")
+        if compute_batch_size not in (1024, 2048, 4096):
+            raise ValueError("compute_batch_size must be one of 1024, 2048, 4096")
+        if not 0 <= combine_start_head_percent <= 100:
+            raise ValueError("combine_start_head_percent must be in [0, 100]")
+        if num_dispatch_sms + num_combine_sms + 1 >= total_sms:
+            raise ValueError("no SMs left for compute")
+        if num_experts % self.group_size:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+
+    def teramoe_autograd(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, W_gateup: torch.Tensor,
+                         W_down: torch.Tensor, num_experts: int, num_dispatch_sms: int = 24, num_combine_sms: int = 24,
+                         total_sms: int = 148, stage: int = 1, dispatch_config: Optional[Config] = None,
+                         combine_config: Optional[Config] = None, grad_topk_weights: Optional[torch.Tensor] = None,
+                         compute_batch_size: int = 2048, combine_start_head_percent: int = 70) -> torch.Tensor:
+        """MoE layer forward with autograd: out[t] = sum_k W_down[e_k] (w_k * silu(g) * u).
+
+        x [T,H] bf16; topk_idx [T,K] (global expert ids, -1 = none); topk_weights [T,K] fp32;
+        W_gateup [E_local, 2I, H] with rows interleaved (g0,u0,g1,u1,...); W_down [E_local, H, I].
+        Gradients flow to x, topk_weights, W_gateup, W_down.  `grad_topk_weights` may be a
+        preallocated fp32 [T,K] tensor that receives d(topk_weights)."""
+        self._check_layer_args(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms, num_combine_sms, total_sms,
+                               stage, compute_batch_size, combine_start_head_percent)
+        opts = {"num_dispatch_sms": num_dispatch_sms, "num_combine_sms": num_combine_sms, "total_sms": total_sms, "stage": stage,
+                "compute_batch_size": compute_batch_size, "combine_start_head_percent": combine_start_head_percent}
+        tw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+        return _TeraMoEFunction.apply(self, x.contiguous(), topk_idx.contiguous(), tw.contiguous(), W_gateup, W_down, num_experts,
+                                      grad_topk_weights, opts)
+
+    def teramoe_forward(self, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms: int = 24,
+                        num_combine_sms: int = 24, total_sms: int = 148, stage: int = 1, dispatch_config: Optional[Config] = None,
+                        combine_config: Optional[Config] = None, compute_batch_size: int = 2048,
+                        combine_start_head_percent: int = 70) -> torch.Tensor:
+        """Inference-only forward (nothing is kept for backward)."""
+        self._check_layer_args(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms, num_combine_sms, total_sms,
+                               stage, compute_batch_size, combine_start_head_percent)
+        opts = {"num_dispatch_sms": num_dispatch_sms, "num_combine_sms": num_combine_sms, "total_sms": total_sms, "stage": stage,
+                "compute_batch_size": compute_batch_size, "combine_start_head_percent": combine_start_head_percent}
+        with torch.no_grad():
+            out, _ = self._drive(self._engine.forward_gen(x.contiguous(), topk_idx.contiguous(), topk_weights.float().contiguous(),
+                                                          W_gateup, W_down, num_experts, keep_for_backward=False, impl=opts))
+        return out

@@ -1,4 +1,217 @@
-// Bindings for routing, communication and the symmetric-memory runtime.
+// Bindings for routing preparation, expert-parallel data movement and the symmetric-memory runtime.
+// Kernels take torch tensors; tables that live in the symmetric arena are passed as tensor views
+// created by SymmetricArena.view (no copy, no ownership).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <pybind11/stl.h>
 #include <torch/extension.h>
 
-void register_more(pybind11::module_& m) { (void)m; }
+#include "comm.h"
+#include "routing.h"
+#include "runtime.h"
+
+namespace {
+
+#define TM_CHECK_CUDA(call)                                                                          \
+    do {                                                                                             \
+        cudaError_t _e = (call);                                                                     \
+        TORCH_CHECK(_e == cudaSuccess, "teramoe_b200: ", #call, " failed: ", cudaGetErrorString(_e)); \
+    } while (0)
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int* i32(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be a contiguous int32 CUDA tensor");
+    return t.data_ptr<int>();
+}
+float* f32(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(), name, " must be a contiguous fp32 CUDA tensor");
+    return t.data_ptr<float>();
+}
+const uint64_t* u64(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt64 && t.is_contiguous(), name, " must be a contiguous int64 CUDA tensor");
+    return reinterpret_cast<const uint64_t*>(t.data_ptr<int64_t>());
+}
+void* bf16(const torch::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.is_contiguous(), name, " must be a contiguous bf16 CUDA tensor");
+    return t.data_ptr();
+}
+int* opt_status(const c10::optional<torch::Tensor>& s) { return s.has_value() ? i32(*s, "status") : nullptr; }
+
+struct TopK {
+    const void* ptr;
+    int is64, T, K;
+};
+TopK topk(const torch::Tensor& idx) {
+    TORCH_CHECK(idx.is_cuda() && idx.is_contiguous() && idx.dim() == 2, "topk_idx must be a contiguous [T,K] CUDA tensor");
+    TORCH_CHECK(idx.scalar_type() == torch::kInt64 || idx.scalar_type() == torch::kInt32, "topk_idx must be int64 or int32");
+    return TopK{idx.data_ptr(), idx.scalar_type() == torch::kInt64 ? 1 : 0, (int)idx.size(0), (int)idx.size(1)};
+}
+
+tmoe::LayoutOut layout_out(const std::vector<torch::Tensor>& t) {
+    TORCH_CHECK(t.size() == 8, "layout tensor list must have 8 entries");
+    tmoe::LayoutOut o;
+    o.expert_total = i32(t[0], "expert_total");
+    o.my_src_off = i32(t[1], "my_src_off");
+    o.seg_off_all = i32(t[2], "seg_off_all");
+    o.my_row_base = i32(t[3], "my_row_base");
+    o.recv_row_base = i32(t[4], "recv_row_base");
+    o.seg_offsets = i32(t[5], "seg_offsets");
+    o.num_mblocks = i32(t[6], "num_mblocks");
+    o.sizes = i32(t[7], "sizes");
+    return o;
+}
+
+tmoe::SymOffsets sym_offsets(const std::vector<int64_t>& v) {
+    TORCH_CHECK(v.size() == 9, "need 9 symmetric offsets");
+    tmoe::SymOffsets so;
+    so.recv_x = v[0]; so.slot_row = v[1]; so.slot_w = v[2]; so.slot_tk = v[3]; so.row_tok = v[4];
+    so.row_land = v[5]; so.row_slots = v[6]; so.landing = v[7]; so.gtw = v[8];
+    return so;
+}
+
+void route_hist(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_hist) {
+    const TopK tk = topk(topk_idx);
+    c10::cuda::CUDAGuard guard(topk_idx.device());
+    TM_CHECK_CUDA(tmoe::route_hist(tk.ptr, tk.is64, tk.T, tk.K, (int)E, (int)N, i32(chunk_hist, "chunk_hist"), cur_stream()));
+}
+
+void route_scan(torch::Tensor chunk_hist, torch::Tensor chunk_base, int64_t num_chunks, int64_t E, int64_t rank, int64_t N,
+                torch::Tensor meta_ptrs, torch::Tensor signal_ptrs, int64_t epoch, c10::optional<torch::Tensor> status) {
+    c10::cuda::CUDAGuard guard(chunk_hist.device());
+    TM_CHECK_CUDA(tmoe::route_scan(i32(chunk_hist, "chunk_hist"), i32(chunk_base, "chunk_base"), (int)num_chunks, (int)E, (int)rank, (int)N,
+                                   u64(meta_ptrs, "meta_ptrs"), u64(signal_ptrs, "signal_ptrs"), (int)epoch, opt_status(status),
+                                   cur_stream()));
+}
+
+void layout_finalize(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, std::vector<torch::Tensor> layout) {
+    c10::cuda::CUDAGuard guard(meta.device());
+    TM_CHECK_CUDA(tmoe::layout_finalize(i32(meta, "meta"), (int)rank, (int)N, (int)E, layout_out(layout), cur_stream()));
+}
+
+void slot_pad_fill(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_row, torch::Tensor slot_w,
+                   torch::Tensor slot_tk, torch::Tensor mblock_expert) {
+    c10::cuda::CUDAGuard guard(seg_offsets.device());
+    TM_CHECK_CUDA(tmoe::slot_pad_fill(i32(seg_offsets, "seg_offsets"), i32(expert_total_local, "expert_total_local"),
+                                      (int)expert_total_local.numel(), i32(slot_row, "slot_row"), f32(slot_w, "slot_w"),
+                                      i32(slot_tk, "slot_tk"), i32(mblock_expert, "mblock_expert"), cur_stream()));
+}
+
+void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_base, std::vector<torch::Tensor> layout,
+                  torch::Tensor send_slot, torch::Tensor send_row, torch::Tensor land_off, torch::Tensor ndst) {
+    const TopK tk = topk(topk_idx);
+    c10::cuda::CUDAGuard guard(topk_idx.device());
+    TM_CHECK_CUDA(tmoe::route_assign(tk.ptr, tk.is64, tk.T, tk.K, (int)E, (int)N, i32(chunk_base, "chunk_base"), layout_out(layout),
+                                     i32(send_slot, "send_slot"), i32(send_row, "send_row"), i32(land_off, "land_off"),
+                                     i32(ndst, "ndst"), cur_stream()));
+}
+
+void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site) {
+    c10::cuda::CUDAGuard guard(signal_ptrs.device());
+    TM_CHECK_CUDA(tmoe::ep_barrier(u64(signal_ptrs, "signal_ptrs"), (int)rank, (int)N, (int)epoch, opt_status(status), (int)site,
+                                   cur_stream()));
+}
+
+void dispatch_push(torch::Tensor x, torch::Tensor topk_idx, torch::Tensor topk_w, int64_t E, int64_t N, torch::Tensor send_slot,
+                   torch::Tensor send_row, torch::Tensor land_off, torch::Tensor arena_ptrs, std::vector<int64_t> offsets,
+                   bool with_meta, int64_t num_blocks) {
+    const TopK tk = topk(topk_idx);
+    TORCH_CHECK(x.dim() == 2 && x.size(0) == tk.T, "x must be [T,H]");
+    c10::cuda::CUDAGuard guard(x.device());
+    TM_CHECK_CUDA(tmoe::dispatch_push(bf16(x, "x"), tk.ptr, tk.is64, f32(topk_w, "topk_weights"), tk.T, tk.K, (int)x.size(1), (int)E, (int)N,
+                                      i32(send_slot, "send_slot"), i32(send_row, "send_row"), i32(land_off, "land_off"),
+                                      u64(arena_ptrs, "arena_ptrs"), sym_offsets(offsets), with_meta ? 1 : 0, (int)num_blocks,
+                                      cur_stream()));
+}
+
+void expand_rows(torch::Tensor rows, torch::Tensor slot_row, torch::Tensor out, int64_t num_slots) {
+    TORCH_CHECK(out.dim() == 2 && out.size(0) >= num_slots && slot_row.numel() >= num_slots && rows.size(1) == out.size(1),
+                "expand_rows: shape mismatch");
+    c10::cuda::CUDAGuard guard(out.device());
+    TM_CHECK_CUDA(tmoe::expand_rows(bf16(rows, "rows"), i32(slot_row, "slot_row"), bf16(out, "out"), (int)num_slots, (int)out.size(1),
+                                    cur_stream()));
+}
+
+void combine_push(torch::Tensor y, torch::Tensor row_slots, torch::Tensor row_land, torch::Tensor recv_row_base, int64_t R, int64_t N,
+                  torch::Tensor arena_ptrs, std::vector<int64_t> offsets, c10::optional<torch::Tensor> droute_part,
+                  c10::optional<torch::Tensor> slot_tk, bool with_payload, int64_t num_blocks) {
+    TORCH_CHECK(row_slots.dim() == 2 && row_slots.size(0) >= R, "row_slots must be [rows,K]");
+    const float* dp = nullptr;
+    const int* stk = nullptr;
+    int n_parts = 0;
+    if (droute_part.has_value()) {
+        TORCH_CHECK(slot_tk.has_value(), "slot_tk is required with droute_part");
+        dp = f32(*droute_part, "droute_part");
+        n_parts = (int)droute_part->size(1);
+        stk = i32(*slot_tk, "slot_tk");
+    }
+    c10::cuda::CUDAGuard guard(y.device());
+    TM_CHECK_CUDA(tmoe::combine_push(bf16(y, "y"), i32(row_slots, "row_slots"), i32(row_land, "row_land"),
+                                     i32(recv_row_base, "recv_row_base"), (int)R, (int)row_slots.size(1), (int)y.size(1), (int)N,
+                                     u64(arena_ptrs, "arena_ptrs"), sym_offsets(offsets), dp, n_parts, stk, with_payload ? 1 : 0, (int)num_blocks,
+                                     cur_stream()));
+}
+
+void combine_reduce(torch::Tensor landing, torch::Tensor land_off, torch::Tensor ndst, torch::Tensor out) {
+    c10::cuda::CUDAGuard guard(out.device());
+    TM_CHECK_CUDA(tmoe::combine_reduce(bf16(landing, "landing"), i32(land_off, "land_off"), i32(ndst, "ndst"), bf16(out, "out"),
+                                       (int)out.size(0), (int)out.size(1), cur_stream()));
+}
+
+torch::Tensor numerics_check(torch::Tensor a, torch::Tensor b) {
+    TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.is_contiguous() && b.is_contiguous() && a.numel() == b.numel() &&
+                a.scalar_type() == b.scalar_type(), "numerics_check: two contiguous CUDA tensors of one dtype and size");
+    TORCH_CHECK(a.scalar_type() == torch::kBFloat16 || a.scalar_type() == torch::kFloat32, "numerics_check: bf16 or fp32");
+    c10::cuda::CUDAGuard guard(a.device());
+    auto out = torch::empty({6}, torch::TensorOptions().dtype(torch::kFloat64).device(a.device()));
+    TM_CHECK_CUDA(tmoe::numerics_check(a.data_ptr(), b.data_ptr(), a.numel(), a.scalar_type() == torch::kBFloat16 ? 1 : 0,
+                                       out.data_ptr<double>(), cur_stream()));
+    return out;
+}
+
+// Tensor view over a range of the local arena.
+torch::Tensor arena_view(tmoe::SymmetricArena& arena, int64_t offset, std::vector<int64_t> sizes, py::object dtype) {
+    const auto st = torch::python::detail::py_object_to_dtype(dtype);
+    int64_t n = 1;
+    for (auto s : sizes) n *= s;
+    TORCH_CHECK(offset >= 0 && offset % 16 == 0, "arena view offset must be a non-negative multiple of 16");
+    TORCH_CHECK((size_t)(offset + n * (int64_t)c10::elementSize(st)) <= arena.bytes(), "arena view out of range");
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return torch::from_blob(reinterpret_cast<void*>(arena.local_ptr() + offset), sizes,
+                            torch::TensorOptions().dtype(st).device(torch::kCUDA, dev));
+}
+
+}  // namespace
+
+void register_more(pybind11::module_& m) {
+    m.def("route_chunk_tokens", &tmoe::route_chunk_tokens);
+    m.def("route_hist", &route_hist);
+    m.def("route_scan", &route_scan);
+    m.def("layout_finalize", &layout_finalize);
+    m.def("slot_pad_fill", &slot_pad_fill);
+    m.def("route_assign", &route_assign);
+    m.def("ep_barrier", &ep_barrier);
+    m.def("dispatch_push", &dispatch_push);
+    m.def("expand_rows", &expand_rows);
+    m.def("combine_push", &combine_push);
+    m.def("combine_reduce", &combine_reduce);
+    m.def("numerics_check", &numerics_check);
+
+    py::class_<tmoe::SymmetricArena>(m, "SymmetricArena")
+        .def(py::init<int, int, size_t>(), py::arg("rank"), py::arg("world"), py::arg("bytes"))
+        .def("export_handle", [](const tmoe::SymmetricArena& a) { return py::bytes(a.export_handle()); })
+        .def("open_peers",
+             [](tmoe::SymmetricArena& a, const std::vector<py::bytes>& hs) {
+                 std::vector<std::string> v;
+                 for (const auto& h : hs) v.emplace_back(static_cast<std::string>(h));
+                 a.open_peers(v);
+             })
+        .def("adopt_peer_pointers", &tmoe::SymmetricArena::adopt_peer_pointers)
+        .def("close", &tmoe::SymmetricArena::close)
+        .def("local_ptr", &tmoe::SymmetricArena::local_ptr)
+        .def("peer_ptrs", &tmoe::SymmetricArena::peer_ptrs)
+        .def("bytes", &tmoe::SymmetricArena::bytes)
+        .def("is_open", &tmoe::SymmetricArena::is_open)
+        .def("view", &arena_view);
+}

@@ -1,0 +1,268 @@
+// Routing preparation: everything that turns topk_idx [T,K] into deterministic destinations.
+//
+//   route_hist      per-chunk histograms over experts, destination ranks and distinct-rank count
+//   route_scan      exclusive scan over chunks -> per-source totals; publishes them to every rank
+//                   (P2P stores into the peers' metadata table) and crosses a bounded barrier
+//   layout_finalize from the all-gathered [ranks, E+ranks+2] table computes, identically on every rank:
+//                   padded per-expert segment offsets of every rank's slot space, this source's
+//                   offset inside every expert segment, row bases of the token-once receive buffers,
+//                   the block->expert map of this rank and the sizes the host needs
+//   route_assign    replays the chunks and gives every (token,k) its slot on the destination rank and
+//                   every (token, destination rank) its row there
+//
+// Slots are deterministic: slot = segment offset of the expert + rows of lower source ranks +
+// rank of the entry among this source's entries for that expert.  The sender therefore writes each
+// token straight to its final place and backward reuses the same places.
+//
+// Reference counterparts: csrc/kernels/layout.cu:9-149 (per-rank / per-expert counts, is_token_in_rank),
+// csrc/kernels/intranode.cu:11-159 (count exchange + prefix matrices) and the receiver-side
+// atomicAdd slot claim at csrc/teramoe/teramoe_orchestrator.cu:1238-1259, which this replaces.
+#include "routing.h"
+
+#include "ptx.cuh"
+
+namespace tmoe {
+
+namespace {
+
+constexpr int kChunkTokens = 128;  // tokens per chunk = threads per block of hist/assign
+
+__device__ __forceinline__ int64_t load_topk(const void* idx, int is64, long i) {
+    return is64 ? reinterpret_cast<const int64_t*>(idx)[i] : (int64_t) reinterpret_cast<const int32_t*>(idx)[i];
+}
+
+// columns of a histogram row: [0,E) experts, [E,E+N) destination ranks, E+N = sum of distinct ranks, E+N+1 = tokens
+__global__ void __launch_bounds__(kChunkTokens)
+route_hist_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist) {
+    extern __shared__ int sh[];
+    const int C = E + N + 2;
+    const int e_local = E / N;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) sh[i] = 0;
+    __syncthreads();
+    const int t = blockIdx.x * kChunkTokens + threadIdx.x;
+    if (t < T) {
+        uint32_t mask = 0;
+        for (int k = 0; k < K; ++k) {
+            const int64_t e = load_topk(topk_idx, is64, (long)t * K + k);
+            if (e >= 0 && e < E) {
+                atomicAdd(&sh[(int)e], 1);
+                mask |= 1u << ((int)e / e_local);
+            }
+        }
+        for (int d = 0; d < N; ++d)
+            if (mask >> d & 1u) atomicAdd(&sh[E + d], 1);
+        atomicAdd(&sh[E + N], __popc(mask));
+        atomicAdd(&sh[E + N + 1], 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < C; i += blockDim.x) chunk_hist[(long)blockIdx.x * C + i] = sh[i];
+}
+
+// One block.  chunk_base[chunk][c] = exclusive prefix over chunks; totals go to row `rank` of the
+// metadata table of every peer; then a barrier over all ranks (skipped when epoch == 0, which the
+// single-device emulation of several ranks uses).
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(const int* chunk_hist, int* chunk_base, int num_chunks, int C, int rank, int N,
+                  const uint64_t* meta_ptrs /* [N] address of each rank's table [N][C] */,
+                  const uint64_t* signal_ptrs /* [N] address of each rank's int[N] signal row */, int epoch, int* status) {
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        int run = 0;
+#pragma unroll 8
+        for (int ch = 0; ch < num_chunks; ++ch) {
+            const int v = chunk_hist[(long)ch * C + c];
+            chunk_base[(long)ch * C + c] = run;
+            run += v;
+        }
+        for (int d = 0; d < N; ++d) reinterpret_cast<int*>(meta_ptrs[d])[(long)rank * C + c] = run;
+    }
+    if (epoch == 0) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < N) {
+        int* peer_sig = reinterpret_cast<int*>(signal_ptrs[threadIdx.x]);
+        st_release_sys(peer_sig + rank, epoch);
+        const int* my_sig = reinterpret_cast<const int*>(signal_ptrs[rank]);
+        if (!wait_flag_ge_sys(my_sig + threadIdx.x, epoch, status, 400 + threadIdx.x)) return;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, LayoutOut o) {
+    const int C = E + N + 2;
+    const int e_local = E / N;
+    __shared__ int sh_spad[64];
+    __shared__ int sh_rows[64];
+    // per-expert totals and this source's offset inside every expert segment
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int tot = 0, before = 0;
+        for (int s = 0; s < N; ++s) {
+            const int v = meta[s * C + e];
+            if (s < rank) before += v;
+            tot += v;
+        }
+        o.expert_total[e] = tot;
+        o.my_src_off[e] = before;
+    }
+    __syncthreads();
+    // padded segment offsets inside every rank's slot space; row bases of every rank's receive buffer
+    if (threadIdx.x < N) {
+        const int d = threadIdx.x;
+        int run = 0;
+        for (int le = 0; le < e_local; ++le) {
+            const int e = d * e_local + le;
+            o.seg_off_all[e] = run;
+            run += (o.expert_total[e] + 127) / 128 * 128;
+        }
+        sh_spad[d] = run;
+        int rows = 0;
+        for (int s = 0; s < N; ++s) {
+            if (s == rank) o.my_row_base[d] = rows;
+            if (d == rank) o.recv_row_base[s] = rows;
+            rows += meta[s * C + E + d];
+        }
+        if (d == rank) o.recv_row_base[N] = rows;
+        sh_rows[d] = rows;
+    }
+    __syncthreads();
+    const int my_spad = sh_spad[rank];
+    if (threadIdx.x == 0) {
+        int rmax = 0, smax = 0, lmax = 0, tmax = 0;
+        for (int d = 0; d < N; ++d) {
+            rmax = max(rmax, sh_rows[d]);
+            smax = max(smax, sh_spad[d]);
+            lmax = max(lmax, meta[d * C + E + N]);
+            tmax = max(tmax, meta[d * C + E + N + 1]);
+        }
+        o.sizes[0] = sh_rows[rank];          // rows received by this rank (token-once)
+        o.sizes[1] = my_spad;                // padded slots of this rank
+        o.sizes[2] = meta[rank * C + E + N]; // combine landing rows of this rank
+        o.sizes[3] = rmax;
+        o.sizes[4] = smax;
+        o.sizes[5] = lmax;
+        o.sizes[6] = my_spad / 128;
+        o.sizes[7] = tmax;
+        o.num_mblocks[0] = my_spad / 128;
+        o.seg_offsets[e_local] = my_spad;
+    }
+    // this rank's segment table
+    for (int le = threadIdx.x; le < e_local; le += blockDim.x) o.seg_offsets[le] = o.seg_off_all[rank * e_local + le];
+}
+
+// Pad slots of this rank's segments (row -1, weight 0) and the block->expert map.  Runs after the
+// host has placed the slot tables (their offsets depend on the sizes computed by layout_finalize).
+__global__ void __launch_bounds__(256)
+slot_pad_fill_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w, int* slot_tk,
+                     int* mblock_expert) {
+    for (int le = blockIdx.x; le < e_local; le += gridDim.x) {
+        const int first = seg_offsets[le] + expert_total_local[le];
+        const int last = seg_offsets[le + 1];
+        for (int b = seg_offsets[le] / 128 + threadIdx.x; b < last / 128; b += blockDim.x) mblock_expert[b] = le;
+        for (int s = first + threadIdx.x; s < last; s += blockDim.x) {
+            slot_row[s] = -1;
+            slot_w[s] = 0.f;
+            slot_tk[s] = -1;
+        }
+    }
+}
+
+// One block per chunk, one thread per token; warps take turns so that ranks inside a chunk follow
+// (warp, k, lane) order.  run[] lives in shared memory and starts from the chunk's scanned base.
+__global__ void __launch_bounds__(kChunkTokens)
+route_assign_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, LayoutOut o,
+                    int* send_slot /* [T,K] */, int* send_row /* [T,N] */, int* land_off /* [T] */, int* ndst /* [T] */) {
+    extern __shared__ int run[];
+    const int C = E + N + 2;
+    const int e_local = E / N;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) run[i] = chunk_base[(long)blockIdx.x * C + i];
+    __syncthreads();
+    const int t = blockIdx.x * kChunkTokens + threadIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t lt = (1u << lane) - 1u;
+    for (int w = 0; w < kChunkTokens / 32; ++w) {
+        if (warp == w) {
+            uint32_t mask = 0;
+            for (int k = 0; k < K; ++k) {
+                int64_t e64 = (t < T) ? load_topk(topk_idx, is64, (long)t * K + k) : -1;
+                const int e = (e64 >= 0 && e64 < E) ? (int)e64 : -1;
+                const uint32_t same = __match_any_sync(0xffffffffu, e);
+                int slot = -1;
+                if (e >= 0) {
+                    const int base = run[e];
+                    slot = o.seg_off_all[e] + o.my_src_off[e] + base + __popc(same & lt);
+                    mask |= 1u << (e / e_local);
+                }
+                __syncwarp();
+                if (e >= 0 && (same & lt) == 0) run[e] += __popc(same);
+                __syncwarp();
+                if (t < T) send_slot[(long)t * K + k] = slot;
+            }
+            for (int d = 0; d < N; ++d) {
+                const bool hit = (mask >> d) & 1u;
+                const uint32_t b = __ballot_sync(0xffffffffu, hit);
+                const int base = run[E + d];
+                if (t < T) send_row[(long)t * N + d] = hit ? o.my_row_base[d] + base + __popc(b & lt) : -1;
+                __syncwarp();
+                if (lane == 0) run[E + d] = base + __popc(b);
+                __syncwarp();
+            }
+            // exclusive scan of distinct-rank counts inside the warp
+            const int n = __popc(mask);
+            int incl = n;
+            for (int s = 1; s < 32; s <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, s);
+                if (lane >= s) incl += v;
+            }
+            const int base = run[E + N];
+            if (t < T) {
+                land_off[t] = base + incl - n;
+                ndst[t] = n;
+            }
+            __syncwarp();
+            if (lane == 31) run[E + N] = base + incl;
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace
+
+int route_chunk_tokens() { return kChunkTokens; }
+
+cudaError_t route_hist(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, cudaStream_t stream) {
+    const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
+    if (chunks == 0) return cudaSuccess;
+    route_hist_kernel<<<chunks, kChunkTokens, (E + N + 2) * sizeof(int), stream>>>(topk_idx, is64, T, K, E, N, chunk_hist);
+    return cudaGetLastError();
+}
+
+cudaError_t route_scan(const int* chunk_hist, int* chunk_base, int num_chunks, int E, int rank, int N, const uint64_t* meta_ptrs,
+                       const uint64_t* signal_ptrs, int epoch, int* status, cudaStream_t stream) {
+    route_scan_kernel<<<1, 1024, 0, stream>>>(chunk_hist, chunk_base, num_chunks, E + N + 2, rank, N, meta_ptrs, signal_ptrs, epoch,
+                                              status);
+    return cudaGetLastError();
+}
+
+cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const LayoutOut& out, cudaStream_t stream) {
+    if (N > 64) return cudaErrorInvalidValue;
+    layout_finalize_kernel<<<1, 1024, 0, stream>>>(meta, rank, N, E, out);
+    return cudaGetLastError();
+}
+
+cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w,
+                          int* slot_tk, int* mblock_expert, cudaStream_t stream) {
+    if (e_local <= 0) return cudaSuccess;
+    slot_pad_fill_kernel<<<e_local < 256 ? e_local : 256, 256, 0, stream>>>(seg_offsets, expert_total_local, e_local, slot_row, slot_w,
+                                                                            slot_tk, mblock_expert);
+    return cudaGetLastError();
+}
+
+cudaError_t route_assign(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, const LayoutOut& out,
+                         int* send_slot, int* send_row, int* land_off, int* ndst, cudaStream_t stream) {
+    const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
+    if (chunks == 0) return cudaSuccess;
+    route_assign_kernel<<<chunks, kChunkTokens, (E + N + 2) * sizeof(int), stream>>>(topk_idx, is64, T, K, E, N, chunk_base, out,
+                                                                                  send_slot, send_row, land_off, ndst);
+    return cudaGetLastError();
+}
+
+}  // namespace tmoe

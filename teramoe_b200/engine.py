@@ -1,0 +1,392 @@
+"""Per-rank pipeline of the expert-parallel MoE layer (forward and backward) as phase generators.
+
+Phase order, forward:   route counts -> [exchange] -> layout -> dispatch push -> [barrier] -> expand,
+gate_up GEMM + SwiGLU, down GEMM, combine push -> [barrier] -> combine reduce.
+Backward re-uses the forward layout (slots are deterministic): dispatch grad rows -> [barrier] ->
+expand, grad_act GEMM + dSwiGLU, dX GEMM, two weight-gradient GEMMs, combine push (+ route-weight
+gradients) -> [barrier] -> reduce.
+
+Kept for backward, as in the reference (csrc/teramoe/teramoe_orchestrator.cu:3653-3678): the
+dispatched X once per received token, the (gate, up) pre-activation per slot, and the slot tables.
+`act` is recomputed from the pre-activation.
+
+On CUDA tensors every step is a hand-written sm_100a kernel (csrc/); on CPU tensors the same steps
+run as plain PyTorch index math (teramoe_b200/layout.py), which is what the CPU tests and the gloo
+multi-process tests exercise.
+
+Reference counterparts: csrc/moe_extension.cpp:1959-2408 (fused forward host path), :2461-2568
+(backward host path), teramoe/buffer.py:710-762 (autograd function).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import layout as L
+from .ops import gemm
+from .parallel.world import EPWorld, _round_up
+
+TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw")
+
+
+@dataclass
+class LayerHandle:
+    """Everything that identifies where rows went; valid for one (topk_idx, num_experts) on one rank."""
+    T: int
+    K: int
+    H: int
+    E: int
+    N: int
+    rank: int
+    rows: int            # token-once rows received by this rank
+    slots: int           # padded slot rows of this rank
+    land_rows: int       # landing rows of this rank (sum of distinct destination ranks of its tokens)
+    maxima: tuple        # (rows, slots, land rows, tokens) maxima over ranks: arena geometry
+    send_slot: torch.Tensor
+    send_row: torch.Tensor
+    land_off: torch.Tensor
+    ndst: torch.Tensor
+    recv_row_base: torch.Tensor
+    seg_offsets: torch.Tensor
+    mblock_expert: torch.Tensor
+    num_mblocks: torch.Tensor
+    expert_total_local: torch.Tensor
+    slot_row: Optional[torch.Tensor] = None
+    slot_w: Optional[torch.Tensor] = None
+    slot_tk: Optional[torch.Tensor] = None
+    row_slots: Optional[torch.Tensor] = None
+    row_land: Optional[torch.Tensor] = None
+    row_tok: Optional[torch.Tensor] = None
+    topk_idx: Optional[torch.Tensor] = None
+    topk_weights: Optional[torch.Tensor] = None
+
+
+@dataclass
+class SavedForBackward:
+    handle: LayerHandle
+    saved_x: torch.Tensor        # [rows, H]
+    preact: torch.Tensor         # [slots, 2I]
+    stats: dict = field(default_factory=dict)
+
+
+def _arena_geometry(maxima, H: int, K: int):
+    rmax, smax, lmax, tmax = [max(int(v), 1) for v in maxima]
+    sizes = {
+        "recv_x": rmax * H * 2, "slot_row": smax * 4, "slot_w": smax * 4, "slot_tk": smax * 4,
+        "row_tok": rmax * 4, "row_land": rmax * 4, "row_slots": rmax * K * 4,
+        "landing": lmax * H * 2, "gtw": tmax * K * 4,
+    }
+    offs, off = {}, 0
+    for name in TABLES:
+        offs[name] = off
+        off += _round_up(sizes[name])
+    return offs, off, (rmax, smax, lmax, tmax)
+
+
+class EPEngine:
+    def __init__(self, world: EPWorld):
+        self.world = world
+        self.is_cuda = world.is_cuda
+        self.ext = world.ext if self.is_cuda else None
+
+    # ------------------------------------------------------------------ table access
+    def _tables(self, offs, maxima, H, K, dtype):
+        w = self.world
+        rmax, smax, lmax, tmax = maxima
+        if self.is_cuda:
+            v = w.data.view
+            return {
+                "recv_x": v(offs["recv_x"], [rmax, H], torch.bfloat16),
+                "slot_row": v(offs["slot_row"], [smax], torch.int32),
+                "slot_w": v(offs["slot_w"], [smax], torch.float32),
+                "slot_tk": v(offs["slot_tk"], [smax], torch.int32),
+                "row_tok": v(offs["row_tok"], [rmax], torch.int32),
+                "row_land": v(offs["row_land"], [rmax], torch.int32),
+                "row_slots": v(offs["row_slots"], [rmax, K], torch.int32),
+                "landing": v(offs["landing"], [lmax, H], torch.bfloat16),
+                "gtw": v(offs["gtw"], [tmax * K], torch.float32),
+            }
+        t = w.cpu_tables
+        shapes = {"recv_x": ((rmax, H), dtype), "slot_row": ((smax,), torch.int32), "slot_w": ((smax,), torch.float32),
+                  "slot_tk": ((smax,), torch.int32), "row_tok": ((rmax,), torch.int32), "row_land": ((rmax,), torch.int32),
+                  "row_slots": ((rmax, K), torch.int32), "landing": ((lmax, H), dtype), "gtw": ((tmax * K,), torch.float32)}
+        for name, (shape, dt) in shapes.items():
+            cur = t.get(name)
+            if cur is None or tuple(cur.shape) != shape or cur.dtype != dt:
+                t[name] = torch.zeros(shape, dtype=dt)
+        return t
+
+    # ------------------------------------------------------------------ routing + dispatch
+    def layout_gen(self, topk_idx: torch.Tensor, num_experts: int):
+        """Counts exchange and deterministic layout.  -> (LayerHandle without receive tables, cuda scratch)."""
+        w = self.world
+        N, rank, E = w.size, w.rank, num_experts
+        T, K = topk_idx.shape
+        if E % N != 0:
+            raise ValueError(f"num_experts ({E}) must be divisible by the number of ranks ({N})")
+        if E + N + 2 > 8192:
+            raise ValueError("too many experts for the metadata row")
+        El = E // N
+        dev = topk_idx.device
+        if not self.is_cuda:
+            row = L.count_row(topk_idx, E, N)
+            meta = yield ("allgather", row)
+            gl = L.global_layout(meta, E, N)
+            sl = L.send_layout(topk_idx, E, N, rank, gl)
+            seg_offsets, me = L.recv_tables(rank, E, N, gl)
+            maxima = (int(gl.rows.max()), int(gl.slots_padded.max()), int(gl.land_rows.max()), int(meta[:, E + N + 1].max()))
+            recv_row_base = torch.cat([gl.row_base[rank], gl.rows[rank:rank + 1]]).to(torch.int32)
+            return LayerHandle(T, K, 0, E, N, rank, int(gl.rows[rank]), int(gl.slots_padded[rank]), int(gl.land_rows[rank]), maxima,
+                               sl.send_slot, sl.send_row, sl.land_off, sl.ndst, recv_row_base, seg_offsets, me,
+                               torch.tensor([me.numel()], dtype=torch.int32),
+                               gl.expert_total.view(N, El)[rank].to(torch.int32).contiguous(), topk_idx=topk_idx)
+        ext = self.ext
+        C = E + N + 2
+        chunk = ext.route_chunk_tokens()
+        chunks = max(1, (T + chunk - 1) // chunk)
+        chunk_hist = torch.zeros(chunks * C, dtype=torch.int32, device=dev)
+        chunk_base = torch.empty(chunks * C, dtype=torch.int32, device=dev)
+        if T > 0:
+            ext.route_hist(topk_idx, E, N, chunk_hist)
+        ext.route_scan(chunk_hist, chunk_base, chunks, E, rank, N, w.ptr_table(w.control, 0, "control_meta"),
+                       w.ptr_table(w.control, w.signal_offset, "control_sig"), 0, w.status)
+        yield ("barrier",)
+        i32 = dict(dtype=torch.int32, device=dev)
+        lay = [torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(N, **i32),
+               torch.empty(N + 1, **i32), torch.empty(El + 1, **i32), torch.empty(1, **i32), torch.empty(8, **i32)]
+        ext.layout_finalize(w.meta_view(C), rank, N, E, lay)
+        w.sizes_host.copy_(lay[7], non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        w.check_status()
+        R, S, Lr, rmax, smax, lmax, nmb, tmax = w.sizes_host.tolist()
+        send_slot = torch.empty(T, K, **i32)
+        send_row = torch.empty(T, N, **i32)
+        land_off = torch.empty(T, **i32)
+        ndst = torch.empty(T, **i32)
+        if T > 0:
+            ext.route_assign(topk_idx, E, N, chunk_base, lay, send_slot, send_row, land_off, ndst)
+        mblock_expert = torch.empty(max(nmb, 1), **i32)
+        h = LayerHandle(T, K, 0, E, N, rank, R, S, Lr, (rmax, smax, lmax, tmax), send_slot, send_row, land_off, ndst, lay[4], lay[5],
+                        mblock_expert, lay[6], lay[0].view(N, El)[rank].contiguous(), topk_idx=topk_idx)
+        return h
+
+    def dispatch_gen(self, h: LayerHandle, x: torch.Tensor, topk_weights: Optional[torch.Tensor], with_meta: bool):
+        """Push rows (and, with_meta, the slot / row tables) to their destination ranks.  After the
+        barrier this returns the table views of this rank."""
+        w = self.world
+        T, H = x.shape
+        K, N, E = h.K, h.N, h.E
+        h.H = H
+        offs, total, maxima = _arena_geometry(h.maxima, H, K)
+        if self.is_cuda:
+            yield ("grow", total)
+        tabs = self._tables(offs, maxima, H, K, x.dtype)
+        if self.is_cuda:
+            ext = self.ext
+            if with_meta:
+                ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert)
+            if T > 0:
+                tw = topk_weights if topk_weights is not None else torch.empty(T, K, dtype=torch.float32, device=x.device)
+                ext.dispatch_push(x, h.topk_idx, tw, E, N, h.send_slot, h.send_row, h.land_off,
+                                  w.ptr_table(w.data, 0, "data"), [offs[n] for n in TABLES], with_meta, 0)
+        else:
+            if with_meta:
+                tabs["slot_row"].fill_(-1)
+                tabs["slot_w"].zero_()
+                tabs["slot_tk"].fill_(-1)
+                tabs["row_slots"].fill_(-1)
+            yield ("push", _cpu_dispatch_writes(h, x, topk_weights, with_meta))
+        yield ("barrier",)
+        return tabs, offs
+
+    def snapshot_tables(self, h: LayerHandle, tabs) -> None:
+        """Copy this rank's receive tables out of the (shared, reused) arena into the handle."""
+        R, S = h.rows, h.slots
+        h.slot_row = tabs["slot_row"][:S].clone()
+        h.slot_w = tabs["slot_w"][:S].clone()
+        h.slot_tk = tabs["slot_tk"][:S].clone()
+        h.row_slots = tabs["row_slots"][:R].clone()
+        h.row_land = tabs["row_land"][:R].clone()
+        h.row_tok = tabs["row_tok"][:R].clone()
+
+    def expand(self, rows: torch.Tensor, h: LayerHandle) -> torch.Tensor:
+        S, H = h.slots, rows.shape[1]
+        out = torch.empty(S, H, dtype=rows.dtype, device=rows.device)
+        if S == 0:
+            return out
+        if self.is_cuda:
+            self.ext.expand_rows(rows, h.slot_row, out, S)
+        else:
+            sr = h.slot_row.long()
+            out.copy_(torch.where((sr >= 0)[:, None], rows[sr.clamp(min=0)], torch.zeros((), dtype=rows.dtype)))
+        return out
+
+    def _combine_push(self, h: LayerHandle, y, offs, parts, with_payload=True):
+        """Launch the push kernel (CUDA) or return the host writes (CPU)."""
+        w = self.world
+        if not self.is_cuda:
+            return _cpu_combine_writes(h, y, parts, with_payload)
+        if h.rows > 0:
+            self.ext.combine_push(y, h.row_slots, h.row_land, h.recv_row_base, h.rows, h.N, w.ptr_table(w.data, 0, "data"),
+                                  [offs[n] for n in TABLES], parts, h.slot_tk if parts is not None else None, with_payload, 0)
+        return None
+
+    def _combine_reduce(self, h: LayerHandle, tabs, dtype, device, want_gtw: bool):
+        T, K, H = h.T, h.K, h.H
+        out = torch.empty(T, H, dtype=dtype, device=device)
+        if T > 0:
+            if self.is_cuda:
+                self.ext.combine_reduce(tabs["landing"], h.land_off, h.ndst, out)
+            else:
+                land = tabs["landing"]
+                lo, nd = h.land_off.long(), h.ndst.long()
+                acc = torch.zeros(T, H, dtype=torch.float32)
+                for j in range(int(nd.max())):
+                    m = nd > j
+                    acc[m] += land[(lo + j)[m]].float()
+                out.copy_(acc.to(dtype))
+        gtw = None
+        if want_gtw:
+            valid = (h.topk_idx >= 0) & (h.topk_idx < h.E)
+            gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=device))
+        return out, gtw
+
+    def combine_gen(self, h: LayerHandle, y: torch.Tensor, tabs, offs, droute_parts: Optional[torch.Tensor] = None):
+        """Sum each received token's local expert outputs and push one row back to its source; after
+        the barrier reduce the landed rows.  -> (out [T,H], gtw [T,K] or None)."""
+        writes = self._combine_push(h, y, offs, droute_parts)
+        if writes is not None:
+            yield ("push", writes)
+        yield ("barrier",)
+        return self._combine_reduce(h, tabs, y.dtype, y.device, droute_parts is not None)
+
+    def combine_rows_gen(self, h: LayerHandle, x: torch.Tensor, recv_topk_weights: Optional[torch.Tensor]):
+        """Un-fused combine of one row per received token (x [rows,H]); optionally carries the
+        received top-k weights back to their source entries.  -> (combined_x [T,H], weights [T,K] | None)."""
+        import copy
+        R, K, dev = h.rows, h.K, x.device
+        if x.shape[0] != R:
+            raise ValueError(f"expected {R} rows (one per received token), got {x.shape[0]}")
+        offs, total, maxima = _arena_geometry(h.maxima, x.shape[1], K)
+        if self.is_cuda:
+            yield ("grow", total)
+        tabs = self._tables(offs, maxima, x.shape[1], K, x.dtype)
+        hh = copy.copy(h)
+        hh.H = x.shape[1]
+        hh.row_slots = torch.full((R, K), -1, dtype=torch.int32, device=dev)
+        if R:
+            hh.row_slots[:, 0] = torch.arange(R, dtype=torch.int32, device=dev)
+        writes = [self._combine_push(hh, x.contiguous(), offs, None)]
+        if recv_topk_weights is not None:
+            # the side channel is indexed by slot: scatter the received weights into slot space
+            rs = h.row_slots.long()
+            valid = rs >= 0
+            kpos = h.slot_tk.long()[rs.clamp(min=0)] % K
+            rr = torch.arange(R, device=dev).view(R, 1).expand(R, K)
+            parts = torch.zeros(max(h.slots, 1), 1, dtype=torch.float32, device=dev)
+            parts[rs[valid], 0] = recv_topk_weights.float()[rr[valid], kpos[valid]]
+            writes.append(self._combine_push(h, x.contiguous(), offs, parts, with_payload=False))
+        for wri in writes:
+            if wri is not None:
+                yield ("push", wri)
+        yield ("barrier",)
+        return self._combine_reduce(hh, tabs, x.dtype, dev, recv_topk_weights is not None)
+
+    # ------------------------------------------------------------------ layer forward / backward
+    def forward_gen(self, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, keep_for_backward=True, impl=None, num_sms=0):
+        w = self.world
+        T, H = x.shape
+        El = num_experts // w.size
+        if W_gateup.shape[0] != El or W_down.shape[0] != El:
+            raise ValueError(f"expected {El} local experts, got W_gateup {tuple(W_gateup.shape)} W_down {tuple(W_down.shape)}")
+        I = W_gateup.shape[1] // 2
+        if W_gateup.shape[2] != H or tuple(W_down.shape[1:]) != (H, I):
+            raise ValueError("weight shapes must be W_gateup [E_local, 2I, H] and W_down [E_local, H, I]")
+        h = yield from self.layout_gen(topk_idx, num_experts)
+        h.topk_weights = topk_weights
+        tabs, offs = yield from self.dispatch_gen(h, x, topk_weights, with_meta=True)
+        self.snapshot_tables(h, tabs)
+        saved_x = tabs["recv_x"][:h.rows].clone()
+        xperm = self.expand(saved_x, h)
+        st = w.status if self.is_cuda else None
+        act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms)
+        del xperm
+        y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms)
+        del act
+        out, _ = yield from self.combine_gen(h, y, tabs, offs)
+        del y
+        saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
+        return out, saved
+
+    def backward_gen(self, saved: SavedForBackward, grad_out, W_gateup, W_down, impl=None, num_sms=0):
+        w = self.world
+        h = saved.handle
+        El = W_gateup.shape[0]
+        st = w.status if self.is_cuda else None
+        tabs, offs = yield from self.dispatch_gen(h, grad_out, None, with_meta=False)
+        dyperm = self.expand(tabs["recv_x"], h)
+        xperm = self.expand(saved.saved_x, h)
+        dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms)
+        dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms)
+        dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms)
+        dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms)
+        del dyperm, xperm, dgu, act_w
+        dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
+        return dx, gtw, dW_gateup, dW_down
+
+
+# ------------------------------------------------------------------------------------------------
+# host (CPU tensor) restatements of the push kernels: produce the writes each peer receives
+# ------------------------------------------------------------------------------------------------
+def _cpu_dispatch_writes(h: LayerHandle, x, topk_weights, with_meta):
+    T, K, N, E = h.T, h.K, h.N, h.E
+    El = E // N
+    idx = h.topk_idx.long()
+    valid = (idx >= 0) & (idx < E)
+    dst_k = torch.where(valid, idx // El, torch.full_like(idx, -1))
+    hit = h.send_row >= 0
+    dord = torch.cumsum(hit.long(), 1) - hit.long()
+    writes = {}
+    for d in range(N):
+        tok = torch.nonzero(hit[:, d], as_tuple=True)[0]
+        rows = h.send_row[tok, d].long()
+        wl = [("recv_x", rows, x[tok])]
+        if with_meta:
+            m = dst_k == d
+            tt, kk = torch.nonzero(m, as_tuple=True)
+            slots = h.send_slot[tt, kk].long()
+            wl.append(("slot_row", slots, h.send_row[tt, d]))
+            wl.append(("slot_w", slots, topk_weights[tt, kk].float()))
+            wl.append(("slot_tk", slots, (tt * K + kk).to(torch.int32)))
+            wl.append(("row_tok", rows, tok.to(torch.int32)))
+            wl.append(("row_land", rows, (h.land_off[tok].long() + dord[tok, d]).to(torch.int32)))
+            pos = torch.cumsum(m.long(), 1) - m.long()
+            rs = torch.full((T, K), -1, dtype=torch.int32)
+            rs[tt, pos[tt, kk]] = h.send_slot[tt, kk]
+            wl.append(("row_slots", rows, rs[tok]))
+        writes[d] = wl
+    return writes
+
+
+def _cpu_combine_writes(h: LayerHandle, y, droute_parts, with_payload=True):
+    N, K = h.N, h.K
+    R = h.rows
+    rs = h.row_slots.long()
+    acc = torch.zeros(R, y.shape[1], dtype=torch.float32)
+    for j in range(K):
+        m = rs[:, j] >= 0
+        acc[m] += y[rs[m, j]].float()
+    acc = acc.to(y.dtype)
+    base = h.recv_row_base.long()
+    writes = {}
+    for s in range(N):
+        r0, r1 = int(base[s]), int(base[s + 1])
+        wl = [("landing", h.row_land[r0:r1].long(), acc[r0:r1])] if with_payload else []
+        if droute_parts is not None:
+            sl = rs[r0:r1].reshape(-1)
+            sl = sl[sl >= 0]
+            wl.append(("gtw", h.slot_tk[sl].long(), droute_parts[sl].sum(1)))
+        writes[s] = wl
+    return writes

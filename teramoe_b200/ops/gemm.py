@@ -30,8 +30,8 @@ def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, 
     """-> (act [S,I], preact [S,2I]).  act = silu(g)*u*row_w, preact = (g,u) interleaved bf16."""
     S, H = xperm.shape
     I = w_gateup.shape[1] // 2
-    act = torch.empty(S, I, dtype=torch.bfloat16, device=xperm.device)
-    preact = torch.empty(S, 2 * I, dtype=torch.bfloat16, device=xperm.device)
+    act = torch.empty(S, I, dtype=xperm.dtype, device=xperm.device)
+    preact = torch.empty(S, 2 * I, dtype=xperm.dtype, device=xperm.device)
     if xperm.is_cuda:
         load_ext().gemm_fwd_gateup(xperm, w_gateup, act, preact, row_w, mblock_expert, num_mblocks, status, num_sms)
     else:
@@ -42,7 +42,7 @@ def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, 
 def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0):
     S, I = act.shape
     H = w_down.shape[1]
-    y = torch.empty(S, H, dtype=torch.bfloat16, device=act.device)
+    y = torch.empty(S, H, dtype=act.dtype, device=act.device)
     if act.is_cuda:
         load_ext().gemm_fwd_down(act, w_down, y, mblock_expert, num_mblocks, status, num_sms)
     else:
@@ -54,8 +54,8 @@ def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, statu
     """-> (dgu [S,2I], act_w [S,I], droute [S] fp32)."""
     S, H = dyperm.shape
     I = w_down.shape[2]
-    dgu = torch.empty(S, 2 * I, dtype=torch.bfloat16, device=dyperm.device)
-    act_w = torch.empty(S, I, dtype=torch.bfloat16, device=dyperm.device)
+    dgu = torch.empty(S, 2 * I, dtype=dyperm.dtype, device=dyperm.device)
+    act_w = torch.empty(S, I, dtype=dyperm.dtype, device=dyperm.device)
     if dyperm.is_cuda:
         parts = torch.empty(S, num_droute_parts(I), dtype=torch.float32, device=dyperm.device)
         load_ext().gemm_bwd_gradact(dyperm, w_down, preact, row_w, dgu, act_w, parts, mblock_expert, num_mblocks, status, num_sms)
@@ -68,7 +68,7 @@ def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, statu
 def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0):
     S = dgu.shape[0]
     H = w_gateup.shape[2]
-    dx = torch.empty(S, H, dtype=torch.bfloat16, device=dgu.device)
+    dx = torch.empty(S, H, dtype=dgu.dtype, device=dgu.device)
     if dgu.is_cuda:
         load_ext().gemm_bwd_dx(dgu, w_gateup, dx, mblock_expert, num_mblocks, status, num_sms)
     else:
@@ -79,14 +79,16 @@ def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0):
 def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0):
     """dW[e] = a[seg_e]^T @ b[seg_e]  -> [E, a.shape[1], b.shape[1]] bf16 (zeros for empty experts)."""
     M, N = a.shape[1], b.shape[1]
-    dw = torch.empty(num_local_experts, M, N, dtype=torch.bfloat16, device=a.device)
+    dw = torch.empty(num_local_experts, M, N, dtype=a.dtype, device=a.device)
+    if a.shape[0] == 0:
+        return dw.zero_()
     if a.is_cuda:
         load_ext().gemm_wgrad(a, b, dw, seg_offsets, status, num_sms)
     else:
         offs = seg_offsets.tolist()
         for e in range(num_local_experts):
             s0, s1 = offs[e], offs[e + 1]
-            dw[e] = (a[s0:s1].float().t() @ b[s0:s1].float()).to(torch.bfloat16)
+            dw[e] = (a[s0:s1].float().t() @ b[s0:s1].float()).to(dw.dtype)
     return dw
 
 

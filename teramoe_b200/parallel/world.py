@@ -1,0 +1,284 @@
+"""Expert-parallel world: ranks, symmetric arenas and the host-side collectives around them.
+
+Three ways to run the same per-rank pipeline (teramoe_b200/engine.py):
+
+* ``EPWorld.from_group(group)``  one process per GPU; arenas are exchanged as CUDA IPC handles through
+  ``torch.distributed`` (NCCL or gloo is only the bootstrap, like teramoe/buffer.py:74-101).
+  With CPU tensors the same class moves data with gloo collectives instead of peer stores.
+* ``EPWorld.single(device)``      one rank, no peers.
+* ``VirtualCluster(n, device)``   n ranks emulated in ONE process on ONE device (or on the CPU), stepped in
+  lock-step phase by phase.  Cross-rank barriers are phase boundaries, so no kernel ever waits for
+  another kernel on the same GPU.  Used by the tests to run the multi-rank index math and the real
+  push kernels without several GPUs.
+
+The pipeline is written as a generator that yields where it needs something from other ranks:
+  ("barrier",)            all ranks reached this point and their peer stores are visible
+  ("allgather", tensor)   -> stacked tensor of all ranks (host path only)
+  ("grow", nbytes)        the data arena must hold nbytes on every rank (all ranks ask together)
+  ("push", {dst: [...]})  host path only: writes into peers' tables
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Generator, List, Optional
+
+import torch
+import torch.distributed as dist
+
+CONTROL_ROW_INTS = 8192          # capacity of one metadata row (E + ranks + 2 ints must fit)
+_ALIGN = 256
+
+
+def _round_up(v: int, a: int = _ALIGN) -> int:
+    return (v + a - 1) // a * a
+
+
+class EPWorld:
+    """One rank's view of the expert-parallel group."""
+
+    def __init__(self, rank: int, size: int, device: torch.device, group=None, virtual_peers: Optional[list] = None):
+        self.rank, self.size, self.device = rank, size, torch.device(device)
+        self.group = group
+        self.virtual_peers = virtual_peers          # list of EPWorld in a VirtualCluster
+        self.is_cuda = self.device.type == "cuda"
+        self.epoch = 0
+        self.control = None
+        self.data = None
+        self.data_bytes = 0
+        self._ptr_cache: Dict[str, torch.Tensor] = {}
+        self.cpu_tables: Dict[str, torch.Tensor] = {}
+        self.closed = False
+        if self.is_cuda:
+            from .._build import load_ext
+            self.ext = load_ext()
+            self.control_bytes = _round_up(size * CONTROL_ROW_INTS * 4 + 4096)
+            self.signal_offset = size * CONTROL_ROW_INTS * 4
+            with torch.cuda.device(self.device):
+                self.control = self.ext.SymmetricArena(rank, size, self.control_bytes)
+            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self.sizes_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def single(cls, device) -> "EPWorld":
+        w = cls(0, 1, device)
+        if w.is_cuda:
+            w.control.adopt_peer_pointers([w.control.local_ptr()])
+        return w
+
+    @classmethod
+    def from_group(cls, group, device) -> "EPWorld":
+        rank, size = dist.get_rank(group), dist.get_world_size(group)
+        w = cls(rank, size, device, group=group)
+        if w.is_cuda:
+            w._open_ipc(w.control)
+        return w
+
+    def _open_ipc(self, arena) -> None:
+        if self.size == 1:
+            arena.adopt_peer_pointers([arena.local_ptr()])
+            return
+        handles: List[Optional[bytes]] = [None] * self.size
+        dist.all_gather_object(handles, bytes(arena.export_handle()), group=self.group)
+        if any(h is None or len(h) != 64 for h in handles):
+            raise RuntimeError("teramoe_b200: malformed IPC handle received during bootstrap")
+        arena.open_peers(handles)
+
+    # ------------------------------------------------------------------ arenas
+    def ptr_table(self, arena, offset: int, key: str) -> torch.Tensor:
+        """Device int64 array with (peer base + offset) for every rank."""
+        k = f"{key}:{arena.local_ptr()}:{offset}"
+        t = self._ptr_cache.get(k)
+        if t is None:
+            t = torch.tensor([p + offset for p in arena.peer_ptrs()], dtype=torch.int64, device=self.device)
+            self._ptr_cache[k] = t
+        return t
+
+    def meta_view(self, C: int) -> torch.Tensor:
+        return self.control.view(0, [self.size * C], torch.int32)
+
+    def ensure_data(self, nbytes: int) -> None:
+        """Real-mode growth of the data arena (collective over the group)."""
+        if nbytes <= self.data_bytes:
+            return
+        assert self.virtual_peers is None, "virtual clusters grow through VirtualCluster.grow"
+        new_bytes = _round_up(int(nbytes * 1.25))
+        torch.cuda.synchronize(self.device)
+        if self.group is not None and self.size > 1:
+            dist.barrier(group=self.group)
+        old = self.data
+        with torch.cuda.device(self.device):
+            self.data = self.ext.SymmetricArena(self.rank, self.size, new_bytes)
+        self._open_ipc(self.data)
+        if old is not None:
+            if self.group is not None and self.size > 1:
+                dist.barrier(group=self.group)
+            old.close()
+        self.data_bytes = new_bytes
+        self._ptr_cache = {k: v for k, v in self._ptr_cache.items() if k.startswith("control")}
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    # ------------------------------------------------------------------ drivers
+    def check_status(self) -> None:
+        if not self.is_cuda:
+            return
+        s = self.status.tolist()
+        if s[0] != 0:
+            self.status.zero_()
+            names = {1: "mbarrier wait", 2: "flag wait", 3: "barrier", 4: "bad argument"}
+            raise RuntimeError(f"teramoe_b200: a device-side wait ran out on rank {self.rank}: {names.get(s[0], s[0])} "
+                               f"(site {s[1]}, block {s[2]}, detail {s[3]})")
+
+    def device_barrier(self, site: int = 500) -> None:
+        if self.size == 1:
+            return
+        ep = self.next_epoch()
+        self.ext.ep_barrier(self.ptr_table(self.control, self.signal_offset, "control_sig"), self.rank, self.size, ep,
+                            self.status, site)
+
+    def drive(self, gen: Generator):
+        """Run a pipeline generator to completion in real (one process per rank) mode."""
+        assert self.virtual_peers is None
+        try:
+            req = next(gen)
+            while True:
+                kind = req[0]
+                if kind == "barrier":
+                    if self.is_cuda:
+                        self.device_barrier()
+                    else:
+                        self._cpu_exchange_pushes()
+                    req = gen.send(None)
+                elif kind == "allgather":
+                    t = req[1]
+                    if self.size == 1:
+                        out = t.unsqueeze(0)
+                    else:
+                        lst = [torch.empty_like(t) for _ in range(self.size)]
+                        dist.all_gather(lst, t, group=self.group)
+                        out = torch.stack(lst)
+                    req = gen.send(out)
+                elif kind == "grow":
+                    self.ensure_data(req[1])
+                    req = gen.send(None)
+                elif kind == "push":
+                    self._pending_pushes = getattr(self, "_pending_pushes", [])
+                    self._pending_pushes.append(req[1])
+                    req = gen.send(None)
+                else:
+                    raise RuntimeError(f"unknown pipeline request {kind}")
+        except StopIteration as stop:
+            return stop.value
+
+    def _cpu_exchange_pushes(self) -> None:
+        pend = getattr(self, "_pending_pushes", [])
+        self._pending_pushes = []
+        merged: Dict[int, list] = {}
+        for p in pend:
+            for d, w in p.items():
+                merged.setdefault(d, []).extend(w)
+        gathered: List[Optional[dict]] = [None] * self.size
+        if self.size == 1:
+            gathered[0] = merged
+        else:
+            dist.all_gather_object(gathered, merged, group=self.group)
+        for src in range(self.size):
+            for (name, idx, val) in gathered[src].get(self.rank, []):
+                apply_write(self.cpu_tables, name, idx, val)
+
+    def close(self) -> None:
+        if self.closed:
+            return
+        self.closed = True
+        if self.is_cuda:
+            torch.cuda.synchronize(self.device)
+            if self.group is not None and self.size > 1 and self.virtual_peers is None:
+                try:
+                    dist.barrier(group=self.group)
+                except Exception:
+                    pass
+            if self.data is not None:
+                self.data.close()
+            self.control.close()
+            self.data = None
+            self._ptr_cache.clear()
+
+
+def apply_write(tables: Dict[str, torch.Tensor], name: str, idx: torch.Tensor, val: torch.Tensor) -> None:
+    if idx.numel():
+        tables[name][idx.long()] = val
+
+
+class VirtualCluster:
+    """n ranks in one process on one device, driven in lock step."""
+
+    def __init__(self, n: int, device="cuda"):
+        self.n = n
+        self.device = torch.device(device)
+        self.worlds: List[EPWorld] = []
+        for r in range(n):
+            self.worlds.append(EPWorld(r, n, self.device, virtual_peers=self.worlds))
+        if self.device.type == "cuda":
+            ptrs = [w.control.local_ptr() for w in self.worlds]
+            for w in self.worlds:
+                w.control.adopt_peer_pointers(ptrs)
+
+    def grow(self, nbytes: int) -> None:
+        if nbytes <= self.worlds[0].data_bytes:
+            return
+        new_bytes = _round_up(int(nbytes * 1.25))
+        torch.cuda.synchronize(self.device)
+        olds = [w.data for w in self.worlds]
+        for w in self.worlds:
+            with torch.cuda.device(self.device):
+                w.data = w.ext.SymmetricArena(w.rank, self.n, new_bytes)
+        ptrs = [w.data.local_ptr() for w in self.worlds]
+        for w in self.worlds:
+            w.data.adopt_peer_pointers(ptrs)
+            w.data_bytes = new_bytes
+            w._ptr_cache = {k: v for k, v in w._ptr_cache.items() if k.startswith("control")}
+        for o in olds:
+            if o is not None:
+                o.close()
+
+    def drive(self, gens: List[Generator]) -> list:
+        """Step one generator per rank in lock step; returns their return values."""
+        results = [None] * self.n
+        reqs = [next(g) for g in gens]
+        done = [False] * self.n
+        while not all(done):
+            kinds = {r[0] for r, d in zip(reqs, done) if not d}
+            assert len(kinds) == 1 and not any(done), f"ranks diverged: {kinds}"
+            kind = kinds.pop()
+            if kind == "barrier":
+                sends = [None] * self.n
+            elif kind == "allgather":
+                stacked = torch.stack([r[1] for r in reqs])
+                sends = [stacked] * self.n
+            elif kind == "grow":
+                self.grow(max(r[1] for r in reqs))
+                sends = [None] * self.n
+            elif kind == "push":
+                for r in reqs:
+                    for d, writes in r[1].items():
+                        for (name, idx, val) in writes:
+                            apply_write(self.worlds[d].cpu_tables, name, idx, val)
+                sends = [None] * self.n
+            else:
+                raise RuntimeError(kind)
+            for i, g in enumerate(gens):
+                try:
+                    reqs[i] = g.send(sends[i])
+                except StopIteration as stop:
+                    results[i] = stop.value
+                    done[i] = True
+        for w in self.worlds:
+            w.check_status()
+        return results
+
+    def close(self) -> None:
+        for w in self.worlds:
+            w.close()

@@ -1,0 +1,100 @@
+"""The sm_100a pipeline on one GPU: routing kernels vs the index-math specification, the layer at
+EP=1 through the public API, and emulated multi-rank runs of the real push kernels."""
+import pytest
+import torch
+
+import teramoe_b200 as tm
+from teramoe_b200 import layout as L
+from teramoe_b200.engine import EPEngine
+from teramoe_b200.parallel.world import VirtualCluster
+from teramoe_b200.utils.numerics import assert_close_bf16, numerics_report
+from helpers import compare, make_problem, oracle, run_virtual
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("N,T,E,K,idx_dtype", [(1, 300, 8, 2, torch.int64), (4, 1000, 32, 6, torch.int32), (8, 515, 64, 8, torch.int64)])
+def test_routing_kernels_match_spec(N, T, E, K, idx_dtype):
+    prob = make_problem(N, T, 64, 64, E, K, seed=7, drop_some=True, empty_expert=2, uneven_tokens=True, dtype=torch.bfloat16, device="cuda")
+    for r in prob["ranks"]:
+        r["idx"] = r["idx"].to(idx_dtype)
+    cluster = VirtualCluster(N, "cuda")
+    try:
+        engines = [EPEngine(w) for w in cluster.worlds]
+        handles = cluster.drive([engines[r].layout_gen(prob["ranks"][r]["idx"], E) for r in range(N)])
+        meta = torch.stack([L.count_row(prob["ranks"][r]["idx"], E, N) for r in range(N)])
+        gl = L.global_layout(meta, E, N)
+        for r, h in enumerate(handles):
+            sl = L.send_layout(prob["ranks"][r]["idx"], E, N, r, gl)
+            assert torch.equal(h.send_slot.cpu(), sl.send_slot)
+            assert torch.equal(h.send_row.cpu(), sl.send_row)
+            assert torch.equal(h.land_off.cpu(), sl.land_off)
+            assert torch.equal(h.ndst.cpu(), sl.ndst)
+            seg, me = L.recv_tables(r, E, N, gl)
+            assert torch.equal(h.seg_offsets.cpu(), seg)
+            assert (h.rows, h.slots, h.land_rows) == (int(gl.rows[r]), int(gl.slots_padded[r]), int(gl.land_rows[r]))
+    finally:
+        cluster.close()
+
+
+@pytest.mark.parametrize("N,T,H,I,E,K", [(1, 256, 256, 512, 8, 2), (2, 300, 512, 256, 8, 4), (4, 200, 256, 384, 16, 8), (8, 96, 128, 128, 32, 8)])
+def test_virtual_cluster_gpu_matches_oracle(N, T, H, I, E, K):
+    prob = make_problem(N, T, H, I, E, K, seed=N + 10, dtype=torch.bfloat16, device="cuda", x_scale=0.5, w_scale=0.05, drop_some=True,
+                        empty_expert=1, uneven_tokens=True)
+    res = run_virtual(prob, "cuda")
+    compare(res, oracle(prob), 2e-2, 2e-2)
+
+
+def test_ep1_public_api_autograd_and_determinism():
+    # reference accuracy protocol: x ~ 0.1 N(0,1), W ~ 0.02 N(0,1); limits max_abs 1e-2, calc_diff 1e-5, cosine 0.99
+    prob = make_problem(1, 512, 1024, 1024, 16, 8, seed=42, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02)
+    r = prob["ranks"][0]
+    buf = tm.Buffer(None, int(64e6), explicitly_destroy=True)
+    outs = []
+    for it in range(2):
+        x = r["x"].clone().requires_grad_(True)
+        w = r["w"].clone().requires_grad_(True)
+        Wg = prob["W_gateup"].clone().requires_grad_(True)
+        Wd = prob["W_down"].clone().requires_grad_(True)
+        out = buf.teramoe_autograd(x, r["idx"], w, Wg, Wd, 16)
+        out.backward(r["go"])
+        outs.append((out.detach(), x.grad, w.grad, Wg.grad, Wd.grad))
+    torch.cuda.synchronize()
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b), "two runs must be bitwise identical"
+    ref = oracle(prob)[0]
+    for name, got in zip(("out", "dx", "dw", "dWg", "dWd"), outs[0]):
+        assert_close_bf16(got.float(), ref[name].cuda().float(), name)
+    buf.destroy()
+
+
+def test_numerics_kernel():
+    a = torch.randn(1000, 333, device="cuda")
+    b = a + 1e-3 * torch.randn_like(a)
+    r = numerics_report(a, b)
+    assert abs(r["max_abs"] - (a - b).abs().max().item()) < 1e-6
+    cos = torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+    assert abs(r["cosine"] - cos) < 1e-6
+    assert abs(r["calc_diff"] - tm.reference.calc_diff(a, b)) < 1e-9
+    r2 = numerics_report(a.bfloat16(), a.bfloat16())
+    assert r2["max_abs"] == 0 and r2["calc_diff"] < 1e-12
+
+
+def test_dispatch_combine_unfused_api():
+    """deepep_dispatch / deepep_combine round trip at EP=1: combine(dispatch(x)) == x * (number of ranks hit = 1)."""
+    T, H, E, K = 200, 256, 8, 4
+    buf = tm.Buffer(None)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda")
+    top = torch.topk(logits, K, dim=1)
+    idx, w = top.indices, torch.softmax(top.values, 1)
+    per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idx, E)
+    assert per_expert.sum().item() == T * K and per_rank.tolist() == [T] and bool(in_rank.all())
+    recv_x, recv_idx, recv_w, counts, handle, _ = buf.deepep_dispatch(x, topk_idx=idx, topk_weights=w, num_tokens_per_expert=per_expert)
+    assert recv_x.shape == (T, H) and counts == per_expert.tolist()
+    assert torch.equal(recv_x, x) and torch.equal(recv_idx, idx) and torch.allclose(recv_w, w)
+    comb, comb_w, _ = buf.deepep_combine(recv_x, handle, topk_weights=recv_w)
+    assert torch.equal(comb, x) and torch.allclose(comb_w, w)
+    # cached handle: payload only
+    recv2, *_ = buf.deepep_dispatch(x * 2, handle=handle)
+    assert torch.equal(recv2, x * 2)
