@@ -7,11 +7,13 @@
 #include <torch/extension.h>
 
 #include "gemm.h"
+#include "launch_count.h"
 
 namespace {
 
 #define TM_CHECK_CUDA(call)                                                                          \
     do {                                                                                             \
+        tmoe::count_launch();                                                                        \
         cudaError_t _e = (call);                                                                     \
         TORCH_CHECK(_e == cudaSuccess, "teramoe_b200: ", #call, " failed: ", cudaGetErrorString(_e)); \
     } while (0)
@@ -112,5 +114,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_bwd_dx", &gemm_bwd_dx);
     m.def("gemm_wgrad", &gemm_wgrad);
     m.def("gemm_num_droute_parts", &tmoe::gemm_num_droute_parts);
+    m.def("launch_count", [] { return tmoe::launch_counter().load(); });
     register_more(m);
 }

@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include "comm.h"
+#include "launch_count.h"
 #include "routing.h"
 #include "runtime.h"
 
@@ -14,6 +15,7 @@ namespace {
 
 #define TM_CHECK_CUDA(call)                                                                          \
     do {                                                                                             \
+        tmoe::count_launch();                                                                        \
         cudaError_t _e = (call);                                                                     \
         TORCH_CHECK(_e == cudaSuccess, "teramoe_b200: ", #call, " failed: ", cudaGetErrorString(_e)); \
     } while (0)

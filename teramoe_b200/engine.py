@@ -375,9 +375,10 @@ def _cpu_combine_writes(h: LayerHandle, y, droute_parts, with_payload=True):
     R = h.rows
     rs = h.row_slots.long()
     acc = torch.zeros(R, y.shape[1], dtype=torch.float32)
-    for j in range(K):
-        m = rs[:, j] >= 0
-        acc[m] += y[rs[m, j]].float()
+    if with_payload:
+        for j in range(K):
+            m = rs[:, j] >= 0
+            acc[m] += y[rs[m, j]].float()
     acc = acc.to(y.dtype)
     base = h.recv_row_base.long()
     writes = {}

@@ -31,11 +31,11 @@ def make_problem(N, T, H, I, E, K, seed=0, dtype=torch.float32, device="cpu", x_
 
 def oracle(prob):
     """fp32 reference over the concatenated tokens of all ranks."""
-    xs = torch.cat([r["x"] for r in prob["ranks"]]).float().cpu().requires_grad_(True)
+    xs = torch.cat([r["x"] for r in prob["ranks"]]).detach().float().cpu().clone().requires_grad_(True)
     idx = torch.cat([r["idx"] for r in prob["ranks"]]).cpu()
-    w = torch.cat([r["w"] for r in prob["ranks"]]).float().cpu().requires_grad_(True)
-    Wg = prob["W_gateup"].float().cpu().requires_grad_(True)
-    Wd = prob["W_down"].float().cpu().requires_grad_(True)
+    w = torch.cat([r["w"] for r in prob["ranks"]]).detach().float().cpu().clone().requires_grad_(True)
+    Wg = prob["W_gateup"].detach().float().cpu().clone().requires_grad_(True)
+    Wd = prob["W_down"].detach().float().cpu().clone().requires_grad_(True)
     go = torch.cat([r["go"] for r in prob["ranks"]]).float().cpu()
     out = moe_reference(xs, idx, w, Wg, Wd)
     out.backward(go)

@@ -1,0 +1,47 @@
+"""Multi-process runs: gloo ranks on CPU (host-side logic), nccl ranks on GPUs (real peer stores)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(backend, case, world, timeout=300, extra_env=None):
+    port = 29600 + (os.getpid() % 300)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        env.update(extra_env or {})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(HERE, "mp_worker.py"), backend, case], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=timeout)
+            outs.append(out)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and f"WORKER_OK {r}" in out, f"rank {r} failed (rc={p.returncode}):\n{out[-3000:]}"
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_gloo_layer(world):
+    _launch("gloo", "layer", world)
+
+
+def test_gloo_mismatched_arguments_raise():
+    _launch("gloo", "mismatch", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_layer_all_gpus():
+    world = torch.cuda.device_count()
+    world = 8 if world >= 8 else 4 if world >= 4 else 2
+    _launch("nccl", "layer", world, timeout=600)
