@@ -39,16 +39,20 @@ cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
 // ---- grouped GEMMs ------------------------------------------------------------------------------
 void gemm_fwd_gateup(torch::Tensor xperm, torch::Tensor w_gateup, torch::Tensor act, torch::Tensor preact, torch::Tensor row_w,
-                     torch::Tensor mblock_expert, torch::Tensor num_mblocks, c10::optional<torch::Tensor> status, int64_t num_sms) {
+                     torch::Tensor mblock_expert, torch::Tensor num_mblocks, c10::optional<torch::Tensor> gather_rows,
+                     c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(xperm, "xperm"); check_bf16(w_gateup, "w_gateup"); check_bf16(act, "act"); check_bf16(preact, "preact");
     check_f32(row_w, "row_w"); check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
-    const int S = xperm.size(0), H = xperm.size(1), E = w_gateup.size(0), I = w_gateup.size(1) / 2;
+    const int H = xperm.size(1), E = w_gateup.size(0), I = w_gateup.size(1) / 2;
+    const int S = gather_rows.has_value() ? (int)gather_rows->numel() : (int)xperm.size(0);
+    const int* gr = nullptr;
+    if (gather_rows.has_value()) { check_i32(*gather_rows, "gather_rows"); gr = gather_rows->data_ptr<int>(); }
     TORCH_CHECK(S % 128 == 0 && w_gateup.size(2) == H && act.size(0) == S && act.size(1) == I && preact.size(0) == S &&
                 preact.size(1) == 2 * I && row_w.numel() == S && mblock_expert.numel() >= S / 128, "gemm_fwd_gateup: shape mismatch");
     c10::cuda::CUDAGuard guard(xperm.device());
     TM_CHECK_CUDA(tmoe::gemm_fwd_gateup(xperm.data_ptr(), w_gateup.data_ptr(), act.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(),
-                                        mblock_expert.data_ptr<int>(), num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status),
-                                        (int)num_sms, cur_stream()));
+                                        mblock_expert.data_ptr<int>(), num_mblocks.data_ptr<int>(), S / 128, H, I, E, gr,
+                                        (int)xperm.size(0), status_ptr(status), (int)num_sms, cur_stream()));
 }
 
 void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
@@ -65,11 +69,14 @@ void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, tor
 
 void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor preact, torch::Tensor row_w, torch::Tensor dgu,
                       torch::Tensor act_w, torch::Tensor droute_part, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
-                      c10::optional<torch::Tensor> status, int64_t num_sms) {
+                      c10::optional<torch::Tensor> gather_rows, c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(dyperm, "dyperm"); check_bf16(w_down, "w_down"); check_bf16(preact, "preact"); check_bf16(dgu, "dgu"); check_bf16(act_w, "act_w");
     check_f32(row_w, "row_w"); check_f32(droute_part, "droute_part");
     check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
-    const int S = dyperm.size(0), H = dyperm.size(1), E = w_down.size(0), I = w_down.size(2);
+    const int H = dyperm.size(1), E = w_down.size(0), I = w_down.size(2);
+    const int S = gather_rows.has_value() ? (int)gather_rows->numel() : (int)dyperm.size(0);
+    const int* gr = nullptr;
+    if (gather_rows.has_value()) { check_i32(*gather_rows, "gather_rows"); gr = gather_rows->data_ptr<int>(); }
     TORCH_CHECK(S % 128 == 0 && w_down.size(1) == H && preact.size(0) == S && preact.size(1) == 2 * I && dgu.size(0) == S &&
                 dgu.size(1) == 2 * I && act_w.size(0) == S && act_w.size(1) == I && row_w.numel() == S &&
                 droute_part.size(0) == S && droute_part.size(1) == tmoe::gemm_num_droute_parts(I) && mblock_expert.numel() >= S / 128,
@@ -77,7 +84,8 @@ void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor 
     c10::cuda::CUDAGuard guard(dyperm.device());
     TM_CHECK_CUDA(tmoe::gemm_bwd_gradact(dyperm.data_ptr(), w_down.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(), dgu.data_ptr(),
                                          act_w.data_ptr(), droute_part.data_ptr<float>(), mblock_expert.data_ptr<int>(),
-                                         num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+                                         num_mblocks.data_ptr<int>(), S / 128, H, I, E, gr, (int)dyperm.size(0), status_ptr(status),
+                                         (int)num_sms, cur_stream()));
 }
 
 void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
@@ -92,14 +100,28 @@ void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm
                                     num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
 }
 
-void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tensor seg_offsets, c10::optional<torch::Tensor> status,
-                int64_t num_sms) {
+void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tensor seg_offsets, c10::optional<torch::Tensor> gather_rows,
+                int64_t gather_operand, c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(dw, "dw"); check_i32(seg_offsets, "seg_offsets");
-    const int S = a.size(0), M = a.size(1), N = b.size(1), E = dw.size(0);
-    TORCH_CHECK(b.size(0) == S && dw.size(1) == M && dw.size(2) == N && seg_offsets.numel() == E + 1, "gemm_wgrad: shape mismatch");
+    const int M = a.size(1), N = b.size(1), E = dw.size(0);
+    const int* gr = nullptr;
+    int S, src_rows = 0;
+    if (gather_rows.has_value() && gather_operand != 0) {
+        check_i32(*gather_rows, "gather_rows");
+        gr = gather_rows->data_ptr<int>();
+        S = (int)gather_rows->numel();
+        TORCH_CHECK(gather_operand == 1 || gather_operand == 2, "gather_operand must be 0, 1 or 2");
+        src_rows = gather_operand == 1 ? (int)a.size(0) : (int)b.size(0);
+        TORCH_CHECK((gather_operand == 1 ? b.size(0) : a.size(0)) == S, "gemm_wgrad: dense operand must have one row per slot");
+    } else {
+        gather_operand = 0;
+        S = (int)a.size(0);
+        TORCH_CHECK(b.size(0) == S, "gemm_wgrad: shape mismatch");
+    }
+    TORCH_CHECK(dw.size(1) == M && dw.size(2) == N && seg_offsets.numel() == E + 1, "gemm_wgrad: shape mismatch");
     c10::cuda::CUDAGuard guard(dw.device());
-    TM_CHECK_CUDA(tmoe::gemm_wgrad(a.data_ptr(), b.data_ptr(), dw.data_ptr(), seg_offsets.data_ptr<int>(), S, M, N, E, status_ptr(status),
-                                   (int)num_sms, cur_stream()));
+    TM_CHECK_CUDA(tmoe::gemm_wgrad(a.data_ptr(), b.data_ptr(), dw.data_ptr(), seg_offsets.data_ptr<int>(), S, M, N, E, gr,
+                                   (int)gather_operand, src_rows, status_ptr(status), (int)num_sms, cur_stream()));
 }
 
 }  // namespace

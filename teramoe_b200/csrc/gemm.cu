@@ -68,6 +68,7 @@ struct GemmArgs {
     int ld_aux;
     const __nv_bfloat16* preact; // bwd grad_act input
     const float* row_w;          // route weight per slot row
+    const int* gather_rows;      // GATHER modes: source row of each slot-space row (-1 = zero row)
     float* droute_part;          // bwd grad_act: [rows, n_parts]
     int n_parts;
     int* status;
@@ -118,7 +119,9 @@ __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* p, const uint32_t* a
     *reinterpret_cast<int4*>(p) = v;
 }
 
-template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
+// GATHER: 0 = operands are dense in slot space; 1 = operand A is gathered row-wise from a row source
+// through gather_rows (TMA tile::gather4); 2 = operand B is gathered (weight-gradient mode only).
+template <bool A_MN, bool B_MN, bool KGROUP, int EPI, int GATHER>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ GemmArgs g) {
@@ -164,49 +167,80 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (elect_one()) {
-            int stage = 0;
-            uint32_t phase = 0;
-            uint32_t issued = 0;
-            bool ok = true;
-            Tile tile;
-            for (int t = blockIdx.x; ok && get_tile<KGROUP>(g, t, num_mblocks, tile); t += gridDim.x) {
-                const int m0 = tile.m_blk * BM;
-                const int n0 = tile.n_blk * BN;
-                for (int kb = 0; kb < tile.nk; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, 100)) { ok = false; break; }
-                    const uint32_t a_dst = smem_base + stage * kStageBytes;
-                    const uint32_t b_dst = a_dst + kAStageBytes;
-                    const uint32_t bar = full_bar(stage);
+        // ------------------------------------------------------------------ TMA producer (whole warp)
+        // Lane 0 arms the barrier and issues the tiled loads; in the gather modes every lane issues the
+        // gather4 copies of its own four rows, whose indices it keeps in registers.
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t issued = 0;
+        bool ok = true;
+        Tile tile;
+        for (int t = blockIdx.x; ok && get_tile<KGROUP>(g, t, num_mblocks, tile); t += gridDim.x) {
+            const int m0 = tile.m_blk * BM;
+            const int n0 = tile.n_blk * BN;
+            int4 ridx = make_int4(-1, -1, -1, -1);
+            if constexpr (GATHER == 1 && !A_MN) ridx = *reinterpret_cast<const int4*>(g.gather_rows + m0 + 4 * lane);
+            if constexpr (GATHER != 0 && KGROUP) {
+                if (tile.nk > 0 && lane < 16) ridx = *reinterpret_cast<const int4*>(g.gather_rows + tile.k0 + 4 * lane);
+            }
+            for (int kb = 0; kb < tile.nk; ++kb) {
+                int4 ridx_next = ridx;
+                if constexpr (GATHER != 0 && KGROUP) {
+                    if (kb + 1 < tile.nk && lane < 16)
+                        ridx_next = *reinterpret_cast<const int4*>(g.gather_rows + tile.k0 + (kb + 1) * BK + 4 * lane);
+                }
+                if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, 100)) { ok = false; break; }
+                const uint32_t a_dst = smem_base + stage * kStageBytes;
+                const uint32_t b_dst = a_dst + kAStageBytes;
+                const uint32_t bar = full_bar(stage);
+                const int k = tile.k0 + kb * BK;
+                if (lane == 0) {
                     mbar_arrive_expect_tx(bar, kStageBytes);
-                    const int k = tile.k0 + kb * BK;
                     if constexpr (!A_MN) {
-                        tma_load_2d(a_dst, &map_a, bar, k, m0);  // box {64 K, 128 rows}
-                    } else {
+                        if constexpr (GATHER != 1) tma_load_2d(a_dst, &map_a, bar, k, m0);  // box {64 K, 128 rows}
+                    } else if constexpr (GATHER != 1) {
 #pragma unroll
                         for (int a = 0; a < BM / 64; ++a) tma_load_2d(a_dst + a * kAtomBytes, &map_a, bar, m0 + 64 * a, k);
                     }
                     if constexpr (!B_MN) {
                         tma_load_2d(b_dst, &map_b, bar, k, tile.group * g.b_group_rows + n0);  // box {64 K, 256 rows}
-                    } else {
+                    } else if constexpr (GATHER != 2) {
                         const int krow = KGROUP ? k : tile.group * g.b_group_rows + k;
 #pragma unroll
                         for (int a = 0; a < BN / 64; ++a) tma_load_2d(b_dst + a * kAtomBytes, &map_b, bar, n0 + 64 * a, krow);
                     }
-                    ++issued;
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
+                if constexpr (GATHER == 1 && !A_MN) {
+                    // 128 rows x 64 K-columns: lane l owns rows 4l..4l+3 (512 bytes of the swizzled tile)
+                    tma_gather4(a_dst + lane * 512, &map_a, bar, k, ridx);
+                }
+                if constexpr (GATHER == 1 && A_MN) {
+                    // 64 K-rows per atom, gathered; lane l < 16 owns K-rows 4l..4l+3 of every 64-wide M atom
+                    if (lane < 16) {
+#pragma unroll
+                        for (int a = 0; a < BM / 64; ++a) tma_gather4(a_dst + a * kAtomBytes + lane * 512, &map_a, bar, m0 + 64 * a, ridx);
+                    }
+                }
+                if constexpr (GATHER == 2) {
+                    if (lane < 16) {
+#pragma unroll
+                        for (int a = 0; a < BN / 64; ++a) tma_gather4(b_dst + a * kAtomBytes + lane * 512, &map_b, bar, n0 + 64 * a, ridx);
+                    }
+                }
+                __syncwarp();
+                ridx = (GATHER != 0 && KGROUP) ? ridx_next : ridx;
+                ++issued;
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
-            if (!ok) {
-                // Gave up: let copies that are still in flight land before the CTA's shared memory is released.
-                const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
-                for (uint32_t i = 0; i < pending; ++i) {
-                    const int s = (stage + kStages - 1 - (int)i) % kStages;
-                    const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
-                    const uint64_t t0 = globaltimer_ns();
-                    while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {}
-                }
+        }
+        if (!ok && lane == 0) {
+            // Gave up: let copies that are still in flight land before the CTA's shared memory is released.
+            const uint32_t pending = issued < (uint32_t)kStages ? issued : (uint32_t)kStages;
+            for (uint32_t i = 0; i < pending; ++i) {
+                const int s = (stage + kStages - 1 - (int)i) % kStages;
+                const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 2000000ull) {}
             }
         }
     } else if (warp == 1) {
@@ -406,10 +440,10 @@ cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
+template <bool A_MN, bool B_MN, bool KGROUP, int EPI, int GATHER>
 cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms,
                    cudaStream_t stream) {
-    auto kern = grouped_gemm_kernel<A_MN, B_MN, KGROUP, EPI>;
+    auto kern = grouped_gemm_kernel<A_MN, B_MN, KGROUP, EPI, GATHER>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -439,12 +473,17 @@ int gemm_num_droute_parts(int I) { return 2 * ((I + BN - 1) / BN); }
 
 cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, void* preact, const float* row_w,
                             const int* mblock_expert, const int* num_mblocks_dev, int max_mblocks, int H, int I,
-                            int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+                            int num_local_experts, const int* gather_rows, int src_rows, int* status, int num_sms,
+                            cudaStream_t stream) {
     if (max_mblocks <= 0) return cudaSuccess;
     if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
     cudaError_t e;
-    if ((e = make_map(&ma, xperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    if (gather_rows != nullptr) {
+        if ((e = make_map(&ma, xperm, (uint64_t)(src_rows > 0 ? src_rows : 1), H, BK, 1)) != cudaSuccess) return e;
+    } else {
+        if ((e = make_map(&ma, xperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    }
     if ((e = make_map(&mb, w_gateup, (uint64_t)num_local_experts * 2 * I, H, BK, BN)) != cudaSuccess) return e;
     GemmArgs g{};
     g.n_total = 2 * I;
@@ -460,7 +499,10 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
     g.ld_aux = 2 * I;
     g.row_w = row_w;
     g.status = status;
-    return launch<false, false, false, kEpiSwiGLU>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    g.gather_rows = gather_rows;
+    if (gather_rows != nullptr)
+        return launch<false, false, false, kEpiSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    return launch<false, false, false, kEpiSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const int* mblock_expert,
@@ -483,18 +525,22 @@ cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const in
     g.d = static_cast<__nv_bfloat16*>(y);
     g.ldd = H;
     g.status = status;
-    return launch<false, false, false, kEpiStore>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    return launch<false, false, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void* preact, const float* row_w, void* dgu,
                              void* act_w, float* droute_part, const int* mblock_expert, const int* num_mblocks_dev,
-                             int max_mblocks, int H, int I, int num_local_experts, int* status, int num_sms,
-                             cudaStream_t stream) {
+                             int max_mblocks, int H, int I, int num_local_experts, const int* gather_rows, int src_rows,
+                             int* status, int num_sms, cudaStream_t stream) {
     if (max_mblocks <= 0) return cudaSuccess;
     if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
     cudaError_t e;
-    if ((e = make_map(&ma, dyperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    if (gather_rows != nullptr) {
+        if ((e = make_map(&ma, dyperm, (uint64_t)(src_rows > 0 ? src_rows : 1), H, BK, 1)) != cudaSuccess) return e;
+    } else {
+        if ((e = make_map(&ma, dyperm, (uint64_t)max_mblocks * BM, H, BK, BM)) != cudaSuccess) return e;
+    }
     // W_down [E*H, I]: K = H rows, N = I contiguous -> MN-major B, box {64 N, 64 K}
     if ((e = make_map(&mb, w_down, (uint64_t)num_local_experts * H, I, 64, BK)) != cudaSuccess) return e;
     GemmArgs g{};
@@ -514,7 +560,10 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
     g.droute_part = droute_part;
     g.n_parts = gemm_num_droute_parts(I);
     g.status = status;
-    return launch<false, true, false, kEpiDSwiGLU>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    g.gather_rows = gather_rows;
+    if (gather_rows != nullptr)
+        return launch<false, true, false, kEpiDSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    return launch<false, true, false, kEpiDSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const int* mblock_expert,
@@ -538,19 +587,22 @@ cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, con
     g.d = static_cast<__nv_bfloat16*>(dxperm);
     g.ldd = H;
     g.status = status;
-    return launch<false, true, false, kEpiStore>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    return launch<false, true, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_offsets, int total_rows, int M, int N,
-                       int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+                       int num_local_experts, const int* gather_rows, int gather_operand, int src_rows, int* status, int num_sms,
+                       cudaStream_t stream) {
     if (num_local_experts <= 0) return cudaSuccess;
     if (M % 8 != 0 || N % 8 != 0) return cudaErrorInvalidValue;
     // The tensor maps must cover at least one row so that encoding succeeds when nothing was received.
     const uint64_t rows = total_rows > 0 ? (uint64_t)total_rows : 1;
     CUtensorMap ma, mb;
     cudaError_t e;
-    if ((e = make_map(&ma, a, rows, M, 64, BK)) != cudaSuccess) return e;
-    if ((e = make_map(&mb, b, rows, N, 64, BK)) != cudaSuccess) return e;
+    const uint64_t srows = src_rows > 0 ? (uint64_t)src_rows : 1;
+    if (gather_rows == nullptr) gather_operand = 0;
+    if ((e = gather_operand == 1 ? make_map(&ma, a, srows, M, 64, 1) : make_map(&ma, a, rows, M, 64, BK)) != cudaSuccess) return e;
+    if ((e = gather_operand == 2 ? make_map(&mb, b, srows, N, 64, 1) : make_map(&mb, b, rows, N, 64, BK)) != cudaSuccess) return e;
     GemmArgs g{};
     g.n_total = N;
     g.num_n_blocks = (N + BN - 1) / BN;
@@ -561,8 +613,11 @@ cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_of
     g.d = static_cast<__nv_bfloat16*>(dw);
     g.ldd = N;
     g.status = status;
-    return launch<true, true, true, kEpiStore>(ma, mb, g, num_local_experts * g.max_mblocks * g.num_n_blocks,
-                                               default_sms(num_sms), stream);
+    g.gather_rows = gather_rows;
+    const int tiles = num_local_experts * g.max_mblocks * g.num_n_blocks;
+    if (gather_operand == 1) return launch<true, true, true, kEpiStore, 1>(ma, mb, g, tiles, default_sms(num_sms), stream);
+    if (gather_operand == 2) return launch<true, true, true, kEpiStore, 2>(ma, mb, g, tiles, default_sms(num_sms), stream);
+    return launch<true, true, true, kEpiStore, 0>(ma, mb, g, tiles, default_sms(num_sms), stream);
 }
 
 }  // namespace tmoe

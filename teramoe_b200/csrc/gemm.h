@@ -26,7 +26,8 @@ namespace tmoe {
 // W_gateup is [E,2I,H] with rows element-interleaved (g0,u0,g1,u1,...).
 cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, void* preact, const float* row_w,
                             const int* mblock_expert, const int* num_mblocks_dev, int max_mblocks, int H, int I,
-                            int num_local_experts, int* status, int num_sms, cudaStream_t stream);
+                            int num_local_experts, const int* gather_rows, int src_rows, int* status, int num_sms,
+                            cudaStream_t stream);
 
 // y[S,H] = act[S,I] . W_down[e]^T          (W_down [E,H,I])
 cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const int* mblock_expert,
@@ -38,8 +39,8 @@ cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const in
 //   droute_part[S, 2*ceil(I/256)] partial sums of ga * silu(g) * u (summed by reduce kernels).
 cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void* preact, const float* row_w, void* dgu,
                              void* act_w, float* droute_part, const int* mblock_expert, const int* num_mblocks_dev,
-                             int max_mblocks, int H, int I, int num_local_experts, int* status, int num_sms,
-                             cudaStream_t stream);
+                             int max_mblocks, int H, int I, int num_local_experts, const int* gather_rows, int src_rows,
+                             int* status, int num_sms, cudaStream_t stream);
 
 // dxperm[S,H] = dgu[S,2I] . W_gateup[e]
 cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const int* mblock_expert,
@@ -48,8 +49,14 @@ cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, con
 
 // dW[e] [M,N] = A[seg_e, M]^T . B[seg_e, N]  for every local expert, seg_e = rows
 // [seg_offsets[e], seg_offsets[e+1]) of slot space (multiples of 128).  Empty segments give zeros.
+//
+// Gather modes (all kernels that take `gather_rows`): instead of a dense slot-space operand the kernel
+// reads row gather_rows[s] of a row source [src_rows, cols] for slot row s (TMA tile::gather4; -1 reads
+// zeros), so the token-once receive buffer feeds the GEMMs without an expanded copy.  For gemm_wgrad
+// `gather_operand` says which operand is the row source: 1 = a, 2 = b, 0 = none.
 cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_offsets, int total_rows, int M, int N,
-                       int num_local_experts, int* status, int num_sms, cudaStream_t stream);
+                       int num_local_experts, const int* gather_rows, int gather_operand, int src_rows, int* status, int num_sms,
+                       cudaStream_t stream);
 
 int gemm_num_droute_parts(int I);
 

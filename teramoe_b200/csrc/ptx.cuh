@@ -146,6 +146,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// Row gather: four rows (r.x, r.y, r.z, r.w) of a 2-D tensor, `box[0]` columns starting at column c0,
+// land as four consecutive rows in shared memory.  The tensor map must have a box of {cols, 1}.
+// Rows that are negative or past the end read as zeros.
+__device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int c0, int4 r) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src_smem), "r"(c0), "r"(c1)

@@ -26,15 +26,24 @@ def num_droute_parts(I: int) -> int:
     return 2 * ((I + 255) // 256)
 
 
-def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, num_sms=0):
-    """-> (act [S,I], preact [S,2I]).  act = silu(g)*u*row_w, preact = (g,u) interleaved bf16."""
-    S, H = xperm.shape
+def _gathered(rows, gather_rows):
+    """Plain restatement of the TMA row gather: slot space <- rows[gather_rows], -1 gives zero rows."""
+    g = gather_rows.long()
+    return torch.where((g >= 0)[:, None], rows[g.clamp(min=0)], torch.zeros((), dtype=rows.dtype, device=rows.device))
+
+
+def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None):
+    """-> (act [S,I], preact [S,2I]).  act = silu(g)*u*row_w, preact = (g,u) interleaved bf16.
+    With `gather_rows` [S], `xperm` is a row source [R,H] and slot row s reads xperm[gather_rows[s]]."""
+    S, H = (gather_rows.numel() if gather_rows is not None else xperm.shape[0]), xperm.shape[1]
     I = w_gateup.shape[1] // 2
     act = torch.empty(S, I, dtype=xperm.dtype, device=xperm.device)
     preact = torch.empty(S, 2 * I, dtype=xperm.dtype, device=xperm.device)
     if xperm.is_cuda:
-        load_ext().gemm_fwd_gateup(xperm, w_gateup, act, preact, row_w, mblock_expert, num_mblocks, status, num_sms)
+        load_ext().gemm_fwd_gateup(xperm, w_gateup, act, preact, row_w, mblock_expert, num_mblocks, gather_rows, status, num_sms)
     else:
+        if gather_rows is not None:
+            xperm = _gathered(xperm, gather_rows)
         ref_fwd_gateup(xperm, w_gateup, row_w, mblock_expert, int(num_mblocks), act, preact)
     return act, preact
 
@@ -50,16 +59,19 @@ def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0):
     return y
 
 
-def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, status=None, num_sms=0):
-    """-> (dgu [S,2I], act_w [S,I], droute [S] fp32)."""
-    S, H = dyperm.shape
+def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None):
+    """-> (dgu [S,2I], act_w [S,I], droute partial sums [S, parts] fp32)."""
+    S, H = (gather_rows.numel() if gather_rows is not None else dyperm.shape[0]), dyperm.shape[1]
     I = w_down.shape[2]
     dgu = torch.empty(S, 2 * I, dtype=dyperm.dtype, device=dyperm.device)
     act_w = torch.empty(S, I, dtype=dyperm.dtype, device=dyperm.device)
     if dyperm.is_cuda:
         parts = torch.empty(S, num_droute_parts(I), dtype=torch.float32, device=dyperm.device)
-        load_ext().gemm_bwd_gradact(dyperm, w_down, preact, row_w, dgu, act_w, parts, mblock_expert, num_mblocks, status, num_sms)
+        load_ext().gemm_bwd_gradact(dyperm, w_down, preact, row_w, dgu, act_w, parts, mblock_expert, num_mblocks, gather_rows, status,
+                                    num_sms)
         return dgu, act_w, parts
+    if gather_rows is not None:
+        dyperm = _gathered(dyperm, gather_rows)
     parts = torch.zeros(S, num_droute_parts(I), dtype=torch.float32)
     ref_bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, int(num_mblocks), dgu, act_w, parts)
     return dgu, act_w, parts
@@ -76,15 +88,21 @@ def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0):
     return dx
 
 
-def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0):
-    """dW[e] = a[seg_e]^T @ b[seg_e]  -> [E, a.shape[1], b.shape[1]] bf16 (zeros for empty experts)."""
+def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0, gather_rows=None, gather_operand=0):
+    """dW[e] = a[seg_e]^T @ b[seg_e]  -> [E, a.shape[1], b.shape[1]] bf16 (zeros for empty experts).
+    gather_operand 1 / 2: operand a / b is a row source read through gather_rows."""
     M, N = a.shape[1], b.shape[1]
     dw = torch.empty(num_local_experts, M, N, dtype=a.dtype, device=a.device)
-    if a.shape[0] == 0:
+    S = gather_rows.numel() if (gather_rows is not None and gather_operand) else a.shape[0]
+    if S == 0 or a.shape[0] == 0 or b.shape[0] == 0:
         return dw.zero_()
     if a.is_cuda:
-        load_ext().gemm_wgrad(a, b, dw, seg_offsets, status, num_sms)
+        load_ext().gemm_wgrad(a, b, dw, seg_offsets, gather_rows, gather_operand if gather_rows is not None else 0, status, num_sms)
     else:
+        if gather_rows is not None and gather_operand == 1:
+            a = _gathered(a, gather_rows)
+        if gather_rows is not None and gather_operand == 2:
+            b = _gathered(b, gather_rows)
         offs = seg_offsets.tolist()
         for e in range(num_local_experts):
             s0, s1 = offs[e], offs[e + 1]

@@ -110,3 +110,36 @@ def test_wgrad(M, N, counts):
         ref = a[o[e]:o[e + 1]].float().t() @ b[o[e]:o[e + 1]].float()
         _close(dw[e], ref, atol=5e-2)
     assert dw[1].abs().max().item() == 0.0 or counts[1] != 0
+
+
+@pytest.mark.parametrize("H,I,counts", CASES)
+def test_gather_modes_match_dense(H, I, counts):
+    """Row-gather operands (TMA gather4 from a token-once row source) give bitwise the dense results."""
+    dev = "cuda"
+    torch.manual_seed(3)
+    E = len(counts)
+    S, offs, me, nmb, valid = _layout(counts, dev)
+    R = max(1, int(valid.sum().item()) // 2 + 3)
+    rows = (torch.randn(R, H, device=dev) * 0.5).to(torch.bfloat16)
+    gidx = torch.where(valid, torch.randint(0, R, (S,), device=dev), torch.full((S,), -1, device=dev)).to(torch.int32)
+    dense = gemm._gathered(rows, gidx).contiguous()
+    wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
+    row_w = torch.rand(S, device=dev) * valid
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    a1, p1 = gemm.fwd_gateup(dense, wgu, row_w, me, nmb, st)
+    a2, p2 = gemm.fwd_gateup(rows, wgu, row_w, me, nmb, st, gather_rows=gidx)
+    assert torch.equal(a1, a2) and torch.equal(p1, p2)
+    d1 = gemm.bwd_gradact(dense, wd, p1, row_w, me, nmb, st)
+    d2 = gemm.bwd_gradact(rows, wd, p1, row_w, me, nmb, st, gather_rows=gidx)
+    for x, y in zip(d1, d2):
+        assert torch.equal(x, y)
+    other = (torch.randn(S, I, device=dev) * 0.5).to(torch.bfloat16) * valid[:, None]
+    w1 = gemm.wgrad(dense, other, offs, E, st)
+    w2 = gemm.wgrad(rows, other, offs, E, st, gather_rows=gidx, gather_operand=1)
+    assert torch.equal(w1, w2)
+    w3 = gemm.wgrad(other, dense, offs, E, st)
+    w4 = gemm.wgrad(other, rows, offs, E, st, gather_rows=gidx, gather_operand=2)
+    assert torch.equal(w3, w4)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0
