@@ -4,6 +4,7 @@
 // Reference counterpart: the pybind block at csrc/moe_extension.cpp:2573-2657.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <pybind11/stl.h>
 #include <torch/extension.h>
 
 #include "gemm.h"
@@ -37,71 +38,88 @@ int* status_ptr(const c10::optional<torch::Tensor>& status) {
 }
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// Python passes the block layout as [mblock_expert, num_mblocks] or, for the CTA-pair kernels,
+// [mblock_expert, num_mblocks, unit_blk, num_units].
+tmoe::MGroupLayout make_layout(const std::vector<torch::Tensor>& t, int S) {
+    TORCH_CHECK(t.size() == 2 || t.size() == 4, "layout must be [mblock_expert, num_mblocks] (+ [unit_blk, num_units])");
+    tmoe::MGroupLayout lay;
+    check_i32(t[0], "mblock_expert"); check_i32(t[1], "num_mblocks");
+    TORCH_CHECK(S % 128 == 0 && t[0].numel() >= S / 128, "mblock_expert too small");
+    lay.mblock_expert = t[0].data_ptr<int>();
+    lay.num_mblocks_dev = t[1].data_ptr<int>();
+    lay.max_mblocks = S / 128;
+    if (t.size() == 4) {
+        check_i32(t[2], "unit_blk"); check_i32(t[3], "num_units");
+        TORCH_CHECK(t[2].numel() >= 2, "unit_blk too small");
+        lay.unit_blk = t[2].data_ptr<int>();
+        lay.num_units_dev = t[3].data_ptr<int>();
+        lay.max_units = (int)t[2].numel() - 1;
+    }
+    return lay;
+}
+
 // ---- grouped GEMMs ------------------------------------------------------------------------------
 void gemm_fwd_gateup(torch::Tensor xperm, torch::Tensor w_gateup, torch::Tensor act, torch::Tensor preact, torch::Tensor row_w,
-                     torch::Tensor mblock_expert, torch::Tensor num_mblocks, c10::optional<torch::Tensor> gather_rows,
+                     std::vector<torch::Tensor> layout, c10::optional<torch::Tensor> gather_rows,
                      c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(xperm, "xperm"); check_bf16(w_gateup, "w_gateup"); check_bf16(act, "act"); check_bf16(preact, "preact");
-    check_f32(row_w, "row_w"); check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    check_f32(row_w, "row_w"); 
     const int H = xperm.size(1), E = w_gateup.size(0), I = w_gateup.size(1) / 2;
     const int S = gather_rows.has_value() ? (int)gather_rows->numel() : (int)xperm.size(0);
     const int* gr = nullptr;
     if (gather_rows.has_value()) { check_i32(*gather_rows, "gather_rows"); gr = gather_rows->data_ptr<int>(); }
     TORCH_CHECK(S % 128 == 0 && w_gateup.size(2) == H && act.size(0) == S && act.size(1) == I && preact.size(0) == S &&
-                preact.size(1) == 2 * I && row_w.numel() == S && mblock_expert.numel() >= S / 128, "gemm_fwd_gateup: shape mismatch");
+                preact.size(1) == 2 * I && row_w.numel() == S, "gemm_fwd_gateup: shape mismatch");
     c10::cuda::CUDAGuard guard(xperm.device());
     TM_CHECK_CUDA(tmoe::gemm_fwd_gateup(xperm.data_ptr(), w_gateup.data_ptr(), act.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(),
-                                        mblock_expert.data_ptr<int>(), num_mblocks.data_ptr<int>(), S / 128, H, I, E, gr,
+                                        make_layout(layout, S), H, I, E, gr,
                                         (int)xperm.size(0), status_ptr(status), (int)num_sms, cur_stream()));
 }
 
-void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, std::vector<torch::Tensor> layout,
                    c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(act, "act"); check_bf16(w_down, "w_down"); check_bf16(y, "y");
-    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    
     const int S = act.size(0), I = act.size(1), E = w_down.size(0), H = w_down.size(1);
-    TORCH_CHECK(S % 128 == 0 && w_down.size(2) == I && y.size(0) == S && y.size(1) == H && mblock_expert.numel() >= S / 128,
+    TORCH_CHECK(S % 128 == 0 && w_down.size(2) == I && y.size(0) == S && y.size(1) == H,
                 "gemm_fwd_down: shape mismatch");
     c10::cuda::CUDAGuard guard(act.device());
-    TM_CHECK_CUDA(tmoe::gemm_fwd_down(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), mblock_expert.data_ptr<int>(),
-                                      num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+    TM_CHECK_CUDA(tmoe::gemm_fwd_down(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
 }
 
 void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor preact, torch::Tensor row_w, torch::Tensor dgu,
-                      torch::Tensor act_w, torch::Tensor droute_part, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+                      torch::Tensor act_w, torch::Tensor droute_part, std::vector<torch::Tensor> layout,
                       c10::optional<torch::Tensor> gather_rows, c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(dyperm, "dyperm"); check_bf16(w_down, "w_down"); check_bf16(preact, "preact"); check_bf16(dgu, "dgu"); check_bf16(act_w, "act_w");
     check_f32(row_w, "row_w"); check_f32(droute_part, "droute_part");
-    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    
     const int H = dyperm.size(1), E = w_down.size(0), I = w_down.size(2);
     const int S = gather_rows.has_value() ? (int)gather_rows->numel() : (int)dyperm.size(0);
     const int* gr = nullptr;
     if (gather_rows.has_value()) { check_i32(*gather_rows, "gather_rows"); gr = gather_rows->data_ptr<int>(); }
     TORCH_CHECK(S % 128 == 0 && w_down.size(1) == H && preact.size(0) == S && preact.size(1) == 2 * I && dgu.size(0) == S &&
                 dgu.size(1) == 2 * I && act_w.size(0) == S && act_w.size(1) == I && row_w.numel() == S &&
-                droute_part.size(0) == S && droute_part.size(1) == tmoe::gemm_num_droute_parts(I) && mblock_expert.numel() >= S / 128,
+                droute_part.size(0) == S && droute_part.size(1) == tmoe::gemm_num_droute_parts(I),
                 "gemm_bwd_gradact: shape mismatch");
     c10::cuda::CUDAGuard guard(dyperm.device());
     TM_CHECK_CUDA(tmoe::gemm_bwd_gradact(dyperm.data_ptr(), w_down.data_ptr(), preact.data_ptr(), row_w.data_ptr<float>(), dgu.data_ptr(),
-                                         act_w.data_ptr(), droute_part.data_ptr<float>(), mblock_expert.data_ptr<int>(),
-                                         num_mblocks.data_ptr<int>(), S / 128, H, I, E, gr, (int)dyperm.size(0), status_ptr(status),
+                                         act_w.data_ptr(), droute_part.data_ptr<float>(), make_layout(layout, S), H, I, E, gr, (int)dyperm.size(0), status_ptr(status),
                                          (int)num_sms, cur_stream()));
 }
 
-void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm, torch::Tensor mblock_expert, torch::Tensor num_mblocks,
+void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm, std::vector<torch::Tensor> layout,
                  c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(dgu, "dgu"); check_bf16(w_gateup, "w_gateup"); check_bf16(dxperm, "dxperm");
-    check_i32(mblock_expert, "mblock_expert"); check_i32(num_mblocks, "num_mblocks");
+    
     const int S = dgu.size(0), I = dgu.size(1) / 2, E = w_gateup.size(0), H = w_gateup.size(2);
-    TORCH_CHECK(S % 128 == 0 && w_gateup.size(1) == 2 * I && dxperm.size(0) == S && dxperm.size(1) == H && mblock_expert.numel() >= S / 128,
+    TORCH_CHECK(S % 128 == 0 && w_gateup.size(1) == 2 * I && dxperm.size(0) == S && dxperm.size(1) == H,
                 "gemm_bwd_dx: shape mismatch");
     c10::cuda::CUDAGuard guard(dgu.device());
-    TM_CHECK_CUDA(tmoe::gemm_bwd_dx(dgu.data_ptr(), w_gateup.data_ptr(), dxperm.data_ptr(), mblock_expert.data_ptr<int>(),
-                                    num_mblocks.data_ptr<int>(), S / 128, H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+    TM_CHECK_CUDA(tmoe::gemm_bwd_dx(dgu.data_ptr(), w_gateup.data_ptr(), dxperm.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
 }
 
 void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tensor seg_offsets, c10::optional<torch::Tensor> gather_rows,
-                int64_t gather_operand, c10::optional<torch::Tensor> status, int64_t num_sms) {
+                int64_t gather_operand, bool cta_pairs, c10::optional<torch::Tensor> status, int64_t num_sms) {
     check_bf16(a, "a"); check_bf16(b, "b"); check_bf16(dw, "dw"); check_i32(seg_offsets, "seg_offsets");
     const int M = a.size(1), N = b.size(1), E = dw.size(0);
     const int* gr = nullptr;
@@ -121,7 +139,7 @@ void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tenso
     TORCH_CHECK(dw.size(1) == M && dw.size(2) == N && seg_offsets.numel() == E + 1, "gemm_wgrad: shape mismatch");
     c10::cuda::CUDAGuard guard(dw.device());
     TM_CHECK_CUDA(tmoe::gemm_wgrad(a.data_ptr(), b.data_ptr(), dw.data_ptr(), seg_offsets.data_ptr<int>(), S, M, N, E, gr,
-                                   (int)gather_operand, src_rows, status_ptr(status), (int)num_sms, cur_stream()));
+                                   (int)gather_operand, src_rows, cta_pairs, status_ptr(status), (int)num_sms, cur_stream()));
 }
 
 }  // namespace

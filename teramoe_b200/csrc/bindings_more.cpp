@@ -92,11 +92,14 @@ void layout_finalize(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, std
 }
 
 void slot_pad_fill(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_row, torch::Tensor slot_w,
-                   torch::Tensor slot_tk, torch::Tensor mblock_expert) {
+                   torch::Tensor slot_tk, torch::Tensor mblock_expert, c10::optional<torch::Tensor> unit_blk,
+                   c10::optional<torch::Tensor> num_units) {
     c10::cuda::CUDAGuard guard(seg_offsets.device());
     TM_CHECK_CUDA(tmoe::slot_pad_fill(i32(seg_offsets, "seg_offsets"), i32(expert_total_local, "expert_total_local"),
                                       (int)expert_total_local.numel(), i32(slot_row, "slot_row"), f32(slot_w, "slot_w"),
-                                      i32(slot_tk, "slot_tk"), i32(mblock_expert, "mblock_expert"), cur_stream()));
+                                      i32(slot_tk, "slot_tk"), i32(mblock_expert, "mblock_expert"),
+                                      unit_blk.has_value() ? i32(*unit_blk, "unit_blk") : nullptr,
+                                      num_units.has_value() ? i32(*num_units, "num_units") : nullptr, cur_stream()));
 }
 
 void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_base, std::vector<torch::Tensor> layout,

@@ -26,98 +26,13 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
-#include <mutex>
-
-#include "ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace tmoe {
 
+using namespace detail;
+
 namespace {
-
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int UK = 16;
-constexpr int kStages = 4;
-constexpr int kAStageBytes = BM * BK * 2;  // 16 KB
-constexpr int kBStageBytes = BN * BK * 2;  // 32 KB
-constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-constexpr int kAtomBytes = 64 * BK * 2;  // one 64(MN) x 64(K) MN-major swizzle atom column: 8 KB
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 128 + 32 * kEpiWarps;
-constexpr int kTmemCols = 512;
-constexpr int kSuperM = 16;  // m-blocks per L2 super-group
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-
-enum Epilogue : int { kEpiStore = 0, kEpiSwiGLU = 1, kEpiDSwiGLU = 2 };
-
-struct GemmArgs {
-    int n_total;                 // columns of D per group
-    int k_total;                 // K of the M-grouped modes
-    int num_n_blocks;            // ceil(n_total / BN)
-    int max_mblocks;             // static bound on m-blocks (M-grouped) or ceil(m_total / BM) (K-grouped)
-    const int* num_mblocks_dev;  // optional device-side live count (M-grouped)
-    const int* mblock_expert;    // [max_mblocks] expert of each m-block (M-grouped)
-    int b_group_rows;            // rows of the B tensor map per expert
-    int num_groups;              // K-grouped: number of experts
-    const int* seg_offsets;      // K-grouped: [num_groups + 1] row offsets, multiples of 128
-    int m_total;                 // K-grouped: rows of dW per expert
-    __nv_bfloat16* d;            // main output
-    int ldd;
-    __nv_bfloat16* aux;          // preact (fwd gate_up) / dGU (bwd grad_act)
-    int ld_aux;
-    const __nv_bfloat16* preact; // bwd grad_act input
-    const float* row_w;          // route weight per slot row
-    const int* gather_rows;      // GATHER modes: source row of each slot-space row (-1 = zero row)
-    float* droute_part;          // bwd grad_act: [rows, n_parts]
-    int n_parts;
-    int* status;
-};
-
-struct Tile {
-    int m_blk, n_blk, group, k0, nk;  // k0: first K row (elements), nk: number of BK blocks
-};
-
-template <bool KGROUP>
-__device__ __forceinline__ bool get_tile(const GemmArgs& g, int t, int num_mblocks, Tile& tile) {
-    if constexpr (!KGROUP) {
-        const int total = num_mblocks * g.num_n_blocks;
-        if (t >= total) return false;
-        const int per_super = kSuperM * g.num_n_blocks;
-        const int super = t / per_super;
-        const int r = t - super * per_super;
-        const int m_first = super * kSuperM;
-        const int m_cnt = min(kSuperM, num_mblocks - m_first);
-        tile.n_blk = r / m_cnt;
-        tile.m_blk = m_first + (r - tile.n_blk * m_cnt);
-        tile.group = g.mblock_expert[tile.m_blk];
-        tile.k0 = 0;
-        tile.nk = g.k_total / BK;
-        return true;
-    } else {
-        const int per_group = g.max_mblocks * g.num_n_blocks;
-        const int total = g.num_groups * per_group;
-        if (t >= total) return false;
-        tile.group = t / per_group;
-        const int r = t - tile.group * per_group;
-        tile.n_blk = r / g.max_mblocks;
-        tile.m_blk = r - tile.n_blk * g.max_mblocks;
-        const int s0 = g.seg_offsets[tile.group];
-        const int s1 = g.seg_offsets[tile.group + 1];
-        tile.k0 = s0;
-        tile.nk = (s1 - s0) / BK;
-        return true;
-    }
-}
-
-__device__ __forceinline__ void store_bf16x8(__nv_bfloat16* p, const uint32_t* acc) {
-    int4 v;
-    v.x = (int)pack_bf16x2(__uint_as_float(acc[0]), __uint_as_float(acc[1]));
-    v.y = (int)pack_bf16x2(__uint_as_float(acc[2]), __uint_as_float(acc[3]));
-    v.z = (int)pack_bf16x2(__uint_as_float(acc[4]), __uint_as_float(acc[5]));
-    v.w = (int)pack_bf16x2(__uint_as_float(acc[6]), __uint_as_float(acc[7]));
-    *reinterpret_cast<int4*>(p) = v;
-}
 
 // GATHER: 0 = operands are dense in slot space; 1 = operand A is gathered row-wise from a row source
 // through gather_rows (TMA tile::gather4); 2 = operand B is gathered (weight-gradient mode only).
@@ -308,89 +223,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 row_ok = (tile.m_blk * BM + r) < g.m_total;
                 row = (long)tile.group * g.m_total + tile.m_blk * BM + r;
             }
-            float w = 0.f;
-            if constexpr (EPI != kEpiStore) w = g.row_w[row];
-            float droute = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < (BN / 2) / 32; ++c) {
-                uint32_t acc[32];
-                tmem_ld_x32(taddr0 + (uint32_t)(c * 32), acc);
-                tmem_ld_wait();
-                const int col = n0 + c * 32;
-                if (zero_tile) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[i] = 0u;
-                }
-                if constexpr (EPI == kEpiStore) {
-                    if (row_ok) {
-                        __nv_bfloat16* dst = g.d + row * g.ldd + col;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            if (col + v * 8 + 8 <= g.n_total) store_bf16x8(dst + v * 8, acc + v * 8);
-                    }
-                } else if constexpr (EPI == kEpiSwiGLU) {
-                    // accumulator columns (2j, 2j+1) = (gate_j, up_j); n_total = 2I
-                    if (col < g.n_total) {
-                        store_bf16x8(g.aux + row * g.ld_aux + col, acc);
-                        store_bf16x8(g.aux + row * g.ld_aux + col + 8, acc + 8);
-                        store_bf16x8(g.aux + row * g.ld_aux + col + 16, acc + 16);
-                        store_bf16x8(g.aux + row * g.ld_aux + col + 24, acc + 24);
-                        uint32_t o[8];
-#pragma unroll
-                        for (int p = 0; p < 8; ++p) {
-                            float a2[2];
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const float gt = __uint_as_float(acc[4 * p + 2 * e]);
-                                const float up = __uint_as_float(acc[4 * p + 2 * e + 1]);
-                                a2[e] = gt / (1.f + expf(-gt)) * up * w;
-                            }
-                            o[p] = pack_bf16x2(a2[0], a2[1]);
-                        }
-                        __nv_bfloat16* dst = g.d + row * g.ldd + (col >> 1);
-                        *reinterpret_cast<int4*>(dst) = make_int4((int)o[0], (int)o[1], (int)o[2], (int)o[3]);
-                        *reinterpret_cast<int4*>(dst + 8) = make_int4((int)o[4], (int)o[5], (int)o[6], (int)o[7]);
-                    }
-                } else {
-                    // accumulator column j = d act_j; n_total = I.  preact holds (g_j, u_j) at [2j, 2j+1].
-                    if (col < g.n_total) {
-                        const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
-                        uint32_t dgu[32];
-                        uint32_t aw[16];
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            const int4 pv = pp[v];
-                            const uint32_t pr[4] = {(uint32_t)pv.x, (uint32_t)pv.y, (uint32_t)pv.z, (uint32_t)pv.w};
-                            float av[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 gu = unpack_bf16x2(pr[e]);
-                                const float ga = __uint_as_float(acc[4 * v + e]);
-                                const float sig = 1.f / (1.f + __expf(-gu.x));
-                                const float s = gu.x * sig;
-                                const float a = s * gu.y;
-                                const float gaw = ga * w;
-                                const float d_up = s * gaw;
-                                const float d_gate = (sig - s * sig + s) * gaw * gu.y;
-                                dgu[4 * v + e] = pack_bf16x2(d_gate, d_up);
-                                av[e] = a * w;
-                                droute += ga * a;
-                            }
-                            aw[2 * v] = pack_bf16x2(av[0], av[1]);
-                            aw[2 * v + 1] = pack_bf16x2(av[2], av[3]);
-                        }
-                        int4* dg = reinterpret_cast<int4*>(g.aux + row * g.ld_aux + 2 * col);
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            dg[v] = make_int4((int)dgu[4 * v], (int)dgu[4 * v + 1], (int)dgu[4 * v + 2], (int)dgu[4 * v + 3]);
-                        int4* da = reinterpret_cast<int4*>(g.d + row * g.ldd + col);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            da[v] = make_int4((int)aw[4 * v], (int)aw[4 * v + 1], (int)aw[4 * v + 2], (int)aw[4 * v + 3]);
-                    }
-                }
-            }
-            if constexpr (EPI == kEpiDSwiGLU) g.droute_part[row * g.n_parts + tile.n_blk * 2 + h] = droute;
+            epilogue_thread<EPI>(g, taddr0, row, row_ok, n0, tile.n_blk * 2 + h, zero_tile);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(as));
@@ -408,38 +241,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-// 2-D bf16 row-major tensor [rows, cols] (cols contiguous), box {box_cols, box_rows}, 128-byte swizzle.
-cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
-    EncodeTiledFn fn = get_encode_fn();
-    if (fn == nullptr) return cudaErrorNotSupported;
-    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0) return cudaErrorInvalidValue;
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
-}
-
 template <bool A_MN, bool B_MN, bool KGROUP, int EPI, int GATHER>
 cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms,
                    cudaStream_t stream) {
@@ -456,25 +257,14 @@ cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs&
     return cudaGetLastError();
 }
 
-int default_sms(int num_sms) {
-    if (num_sms > 0) return num_sms;
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return cached;
-}
-
 }  // namespace
 
 int gemm_num_droute_parts(int I) { return 2 * ((I + BN - 1) / BN); }
 
 cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, void* preact, const float* row_w,
-                            const int* mblock_expert, const int* num_mblocks_dev, int max_mblocks, int H, int I,
-                            int num_local_experts, const int* gather_rows, int src_rows, int* status, int num_sms,
+                            const MGroupLayout& lay, int H, int I, int num_local_experts, const int* gather_rows, int src_rows, int* status, int num_sms,
                             cudaStream_t stream) {
+    const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
@@ -490,8 +280,11 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
     g.k_total = H;
     g.num_n_blocks = (2 * I + BN - 1) / BN;
     g.max_mblocks = max_mblocks;
-    g.num_mblocks_dev = num_mblocks_dev;
-    g.mblock_expert = mblock_expert;
+    g.num_mblocks_dev = lay.num_mblocks_dev;
+    g.mblock_expert = lay.mblock_expert;
+    g.unit_blk = lay.unit_blk;
+    g.num_units_dev = lay.num_units_dev;
+    g.max_units = lay.max_units;
     g.b_group_rows = 2 * I;
     g.d = static_cast<__nv_bfloat16*>(act);
     g.ldd = I;
@@ -500,14 +293,16 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
     g.row_w = row_w;
     g.status = status;
     g.gather_rows = gather_rows;
+    if (lay.unit_blk != nullptr && gather_rows == nullptr)
+        return gemm2_mgroup(0, xperm, w_gateup, g, max_mblocks * BM, H, num_local_experts * 2 * I, H, num_sms, stream);
     if (gather_rows != nullptr)
         return launch<false, false, false, kEpiSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
     return launch<false, false, false, kEpiSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
-cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const int* mblock_expert,
-                          const int* num_mblocks_dev, int max_mblocks, int H, int I, int num_local_experts, int* status,
-                          int num_sms, cudaStream_t stream) {
+cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const MGroupLayout& lay, int H, int I,
+                          int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+    const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if (I % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
@@ -519,19 +314,23 @@ cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const in
     g.k_total = I;
     g.num_n_blocks = (H + BN - 1) / BN;
     g.max_mblocks = max_mblocks;
-    g.num_mblocks_dev = num_mblocks_dev;
-    g.mblock_expert = mblock_expert;
+    g.num_mblocks_dev = lay.num_mblocks_dev;
+    g.mblock_expert = lay.mblock_expert;
+    g.unit_blk = lay.unit_blk;
+    g.num_units_dev = lay.num_units_dev;
+    g.max_units = lay.max_units;
     g.b_group_rows = H;
     g.d = static_cast<__nv_bfloat16*>(y);
     g.ldd = H;
     g.status = status;
+    if (lay.unit_blk != nullptr) return gemm2_mgroup(1, act, w_down, g, max_mblocks * BM, I, num_local_experts * H, I, num_sms, stream);
     return launch<false, false, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void* preact, const float* row_w, void* dgu,
-                             void* act_w, float* droute_part, const int* mblock_expert, const int* num_mblocks_dev,
-                             int max_mblocks, int H, int I, int num_local_experts, const int* gather_rows, int src_rows,
+                             void* act_w, float* droute_part, const MGroupLayout& lay, int H, int I, int num_local_experts, const int* gather_rows, int src_rows,
                              int* status, int num_sms, cudaStream_t stream) {
+    const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if (H % BK != 0 || I % 32 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
@@ -548,8 +347,11 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
     g.k_total = H;
     g.num_n_blocks = (I + BN - 1) / BN;
     g.max_mblocks = max_mblocks;
-    g.num_mblocks_dev = num_mblocks_dev;
-    g.mblock_expert = mblock_expert;
+    g.num_mblocks_dev = lay.num_mblocks_dev;
+    g.mblock_expert = lay.mblock_expert;
+    g.unit_blk = lay.unit_blk;
+    g.num_units_dev = lay.num_units_dev;
+    g.max_units = lay.max_units;
     g.b_group_rows = H;
     g.d = static_cast<__nv_bfloat16*>(act_w);
     g.ldd = I;
@@ -561,14 +363,16 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
     g.n_parts = gemm_num_droute_parts(I);
     g.status = status;
     g.gather_rows = gather_rows;
+    if (lay.unit_blk != nullptr && gather_rows == nullptr)
+        return gemm2_mgroup(2, dyperm, w_down, g, max_mblocks * BM, H, num_local_experts * H, I, num_sms, stream);
     if (gather_rows != nullptr)
         return launch<false, true, false, kEpiDSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
     return launch<false, true, false, kEpiDSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
-cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const int* mblock_expert,
-                        const int* num_mblocks_dev, int max_mblocks, int H, int I, int num_local_experts, int* status,
-                        int num_sms, cudaStream_t stream) {
+cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const MGroupLayout& lay, int H, int I,
+                        int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+    const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if ((2 * I) % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
     CUtensorMap ma, mb;
@@ -581,18 +385,23 @@ cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, con
     g.k_total = 2 * I;
     g.num_n_blocks = (H + BN - 1) / BN;
     g.max_mblocks = max_mblocks;
-    g.num_mblocks_dev = num_mblocks_dev;
-    g.mblock_expert = mblock_expert;
+    g.num_mblocks_dev = lay.num_mblocks_dev;
+    g.mblock_expert = lay.mblock_expert;
+    g.unit_blk = lay.unit_blk;
+    g.num_units_dev = lay.num_units_dev;
+    g.max_units = lay.max_units;
     g.b_group_rows = 2 * I;
     g.d = static_cast<__nv_bfloat16*>(dxperm);
     g.ldd = H;
     g.status = status;
+    if (lay.unit_blk != nullptr)
+        return gemm2_mgroup(3, dgu, w_gateup, g, max_mblocks * BM, 2 * I, num_local_experts * 2 * I, H, num_sms, stream);
     return launch<false, true, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
 cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_offsets, int total_rows, int M, int N,
-                       int num_local_experts, const int* gather_rows, int gather_operand, int src_rows, int* status, int num_sms,
-                       cudaStream_t stream) {
+                       int num_local_experts, const int* gather_rows, int gather_operand, int src_rows, bool cta_pairs, int* status,
+                       int num_sms, cudaStream_t stream) {
     if (num_local_experts <= 0) return cudaSuccess;
     if (M % 8 != 0 || N % 8 != 0) return cudaErrorInvalidValue;
     // The tensor maps must cover at least one row so that encoding succeeds when nothing was received.
@@ -615,6 +424,7 @@ cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_of
     g.status = status;
     g.gather_rows = gather_rows;
     const int tiles = num_local_experts * g.max_mblocks * g.num_n_blocks;
+    if (cta_pairs && gather_operand == 0 && total_rows > 0) return gemm2_wgrad(a, b, g, total_rows, M, N, num_sms, stream);
     if (gather_operand == 1) return launch<true, true, true, kEpiStore, 1>(ma, mb, g, tiles, default_sms(num_sms), stream);
     if (gather_operand == 2) return launch<true, true, true, kEpiStore, 2>(ma, mb, g, tiles, default_sms(num_sms), stream);
     return launch<true, true, true, kEpiStore, 0>(ma, mb, g, tiles, default_sms(num_sms), stream);

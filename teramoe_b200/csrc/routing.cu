@@ -148,19 +148,38 @@ layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, Lay
     for (int le = threadIdx.x; le < e_local; le += blockDim.x) o.seg_offsets[le] = o.seg_off_all[rank * e_local + le];
 }
 
-// Pad slots of this rank's segments (row -1, weight 0) and the block->expert map.  Runs after the
-// host has placed the slot tables (their offsets depend on the sizes computed by layout_finalize).
+// Pad slots of this rank's segments (row -1, weight 0), the block->expert map and the unit table of
+// the CTA-pair GEMMs (a unit = one or two consecutive 128-row blocks of one expert; unit_blk[u] is
+// its first block, unit_blk[num_units] the block count).  Runs after the host has placed the slot
+// tables (their offsets depend on the sizes computed by layout_finalize).
 __global__ void __launch_bounds__(256)
 slot_pad_fill_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w, int* slot_tk,
-                     int* mblock_expert) {
+                     int* mblock_expert, int* unit_blk, int* num_units) {
+    __shared__ int unit_base;
     for (int le = blockIdx.x; le < e_local; le += gridDim.x) {
         const int first = seg_offsets[le] + expert_total_local[le];
         const int last = seg_offsets[le + 1];
-        for (int b = seg_offsets[le] / 128 + threadIdx.x; b < last / 128; b += blockDim.x) mblock_expert[b] = le;
+        const int blk0 = seg_offsets[le] / 128, blk1 = last / 128;
+        for (int b = blk0 + threadIdx.x; b < blk1; b += blockDim.x) mblock_expert[b] = le;
         for (int s = first + threadIdx.x; s < last; s += blockDim.x) {
             slot_row[s] = -1;
             slot_w[s] = 0.f;
             slot_tk[s] = -1;
+        }
+        if (unit_blk != nullptr) {
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int base = 0;
+                for (int j = 0; j < le; ++j) base += ((seg_offsets[j + 1] - seg_offsets[j]) / 128 + 1) / 2;
+                unit_base = base;
+            }
+            __syncthreads();
+            const int nu = (blk1 - blk0 + 1) / 2;
+            for (int i = threadIdx.x; i < nu; i += blockDim.x) unit_blk[unit_base + i] = blk0 + 2 * i;
+            if (le == e_local - 1 && threadIdx.x == 0) {
+                unit_blk[unit_base + nu] = blk1;
+                num_units[0] = unit_base + nu;
+            }
         }
     }
 }
@@ -249,10 +268,10 @@ cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const Layou
 }
 
 cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w,
-                          int* slot_tk, int* mblock_expert, cudaStream_t stream) {
+                          int* slot_tk, int* mblock_expert, int* unit_blk, int* num_units, cudaStream_t stream) {
     if (e_local <= 0) return cudaSuccess;
     slot_pad_fill_kernel<<<e_local < 256 ? e_local : 256, 256, 0, stream>>>(seg_offsets, expert_total_local, e_local, slot_row, slot_w,
-                                                                            slot_tk, mblock_expert);
+                                                                            slot_tk, mblock_expert, unit_blk, num_units);
     return cudaGetLastError();
 }
 

@@ -24,7 +24,7 @@ cudaError_t route_scan(const int* chunk_hist, int* chunk_base, int num_chunks, i
                        const uint64_t* signal_ptrs, int epoch, int* status, cudaStream_t stream);
 cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const LayoutOut& out, cudaStream_t stream);
 cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w,
-                          int* slot_tk, int* mblock_expert, cudaStream_t stream);
+                          int* slot_tk, int* mblock_expert, int* unit_blk, int* num_units, cudaStream_t stream);
 cudaError_t route_assign(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, const LayoutOut& out,
                          int* send_slot, int* send_row, int* land_off, int* ndst, cudaStream_t stream);
 

@@ -34,6 +34,9 @@ from .parallel.world import EPWorld, _round_up
 # copy per ~70 cycles per SM, which caps the gate_up GEMM at 457 TFLOP/s against 1400 with a dense
 # operand, while the expand pass costs 0.3 ms.  So the expanded copy is the default.
 USE_TMA_GATHER = os.environ.get("TERAMOE_TMA_GATHER", "0") == "1"
+# CTA-pair (tcgen05 cta_group::2, 256x256 tiles) GEMM kernels.  Bitwise equal to the one-CTA kernels
+# but measured slower so far (see csrc/gemm2.cu), hence off unless asked for.
+USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "0") == "1"
 
 TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw")
 
@@ -60,6 +63,8 @@ class LayerHandle:
     mblock_expert: torch.Tensor
     num_mblocks: torch.Tensor
     expert_total_local: torch.Tensor
+    unit_blk: Optional[torch.Tensor] = None      # CTA-pair GEMMs: first block of every unit (+ sentinel)
+    num_units: Optional[torch.Tensor] = None
     slot_row: Optional[torch.Tensor] = None
     slot_w: Optional[torch.Tensor] = None
     slot_tk: Optional[torch.Tensor] = None
@@ -175,8 +180,11 @@ class EPEngine:
         if T > 0:
             ext.route_assign(topk_idx, E, N, chunk_base, lay, send_slot, send_row, land_off, ndst)
         mblock_expert = torch.empty(max(nmb, 1), **i32)
+        unit_blk = torch.zeros((nmb + El) // 2 + 2, **i32)
+        num_units = torch.zeros(1, **i32)
         h = LayerHandle(T, K, 0, E, N, rank, R, S, Lr, (rmax, smax, lmax, tmax), send_slot, send_row, land_off, ndst, lay[4], lay[5],
                         mblock_expert, lay[6], lay[0].view(N, El)[rank].contiguous(), topk_idx=topk_idx)
+        h.unit_blk, h.num_units = unit_blk, num_units
         return h
 
     def dispatch_gen(self, h: LayerHandle, x: torch.Tensor, topk_weights: Optional[torch.Tensor], with_meta: bool):
@@ -193,7 +201,8 @@ class EPEngine:
         if self.is_cuda:
             ext = self.ext
             if with_meta:
-                ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert)
+                ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert,
+                                  h.unit_blk, h.num_units)
             if T > 0:
                 tw = topk_weights if topk_weights is not None else torch.empty(T, K, dtype=torch.float32, device=x.device)
                 ext.dispatch_push(x, h.topk_idx, tw, E, N, h.send_slot, h.send_row, h.land_off,
@@ -317,13 +326,14 @@ class EPEngine:
         self.snapshot_tables(h, tabs)
         saved_x = tabs["recv_x"][:h.rows].clone()
         st = w.status if self.is_cuda else None
+        units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
         if USE_TMA_GATHER:
             act, preact = gemm.fwd_gateup(saved_x, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, gather_rows=h.slot_row)
         else:
             xperm = self.expand(saved_x, h)
-            act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms)
+            act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del xperm
-        y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms)
+        y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
         del act
         out, _ = yield from self.combine_gen(h, y, tabs, offs)
         del y
@@ -344,13 +354,16 @@ class EPEngine:
             dW_down = gemm.wgrad(dy_rows, act_w, h.seg_offsets, El, st, num_sms, gather_rows=h.slot_row, gather_operand=1)
             dW_gateup = gemm.wgrad(dgu, saved.saved_x, h.seg_offsets, El, st, num_sms, gather_rows=h.slot_row, gather_operand=2)
         else:
+            units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
+            pairs = units is not None
             dyperm = self.expand(tabs["recv_x"], h)
-            dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms)
-            dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms)
-            dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms)
+            dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
+                                                 units=units)
+            dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
+            dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del dyperm
             xperm = self.expand(saved.saved_x, h)
-            dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms)
+            dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del xperm
         del dgu, act_w
         dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)

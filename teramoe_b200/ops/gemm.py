@@ -26,13 +26,32 @@ def num_droute_parts(I: int) -> int:
     return 2 * ((I + 255) // 256)
 
 
+def _lay(mblock_expert, num_mblocks, units):
+    """Block layout list for the bindings; `units` = (unit_blk, num_units) selects the CTA-pair kernels."""
+    return [mblock_expert, num_mblocks] + (list(units) if units is not None else [])
+
+
+def make_units(mblock_expert: torch.Tensor):
+    """Host-side unit table (tests): pairs of consecutive blocks of one expert -> (unit_blk, num_units)."""
+    me = mblock_expert.tolist()
+    ub, b = [], 0
+    while b < len(me):
+        e, start = me[b], b
+        while b < len(me) and me[b] == e:
+            b += 1
+        ub += list(range(start, b, 2))
+    ub.append(len(me))
+    dev = mblock_expert.device
+    return torch.tensor(ub, dtype=torch.int32, device=dev), torch.tensor([len(ub) - 1], dtype=torch.int32, device=dev)
+
+
 def _gathered(rows, gather_rows):
     """Plain restatement of the TMA row gather: slot space <- rows[gather_rows], -1 gives zero rows."""
     g = gather_rows.long()
     return torch.where((g >= 0)[:, None], rows[g.clamp(min=0)], torch.zeros((), dtype=rows.dtype, device=rows.device))
 
 
-def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None):
+def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None, units=None):
     """-> (act [S,I], preact [S,2I]).  act = silu(g)*u*row_w, preact = (g,u) interleaved bf16.
     With `gather_rows` [S], `xperm` is a row source [R,H] and slot row s reads xperm[gather_rows[s]]."""
     S, H = (gather_rows.numel() if gather_rows is not None else xperm.shape[0]), xperm.shape[1]
@@ -40,7 +59,7 @@ def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, 
     act = torch.empty(S, I, dtype=xperm.dtype, device=xperm.device)
     preact = torch.empty(S, 2 * I, dtype=xperm.dtype, device=xperm.device)
     if xperm.is_cuda:
-        load_ext().gemm_fwd_gateup(xperm, w_gateup, act, preact, row_w, mblock_expert, num_mblocks, gather_rows, status, num_sms)
+        load_ext().gemm_fwd_gateup(xperm, w_gateup, act, preact, row_w, _lay(mblock_expert, num_mblocks, units), gather_rows, status, num_sms)
     else:
         if gather_rows is not None:
             xperm = _gathered(xperm, gather_rows)
@@ -48,18 +67,18 @@ def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, 
     return act, preact
 
 
-def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0):
+def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0, units=None):
     S, I = act.shape
     H = w_down.shape[1]
     y = torch.empty(S, H, dtype=act.dtype, device=act.device)
     if act.is_cuda:
-        load_ext().gemm_fwd_down(act, w_down, y, mblock_expert, num_mblocks, status, num_sms)
+        load_ext().gemm_fwd_down(act, w_down, y, _lay(mblock_expert, num_mblocks, units), status, num_sms)
     else:
         ref_mgroup(act, w_down.transpose(1, 2), mblock_expert, int(num_mblocks), y)
     return y
 
 
-def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None):
+def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, status=None, num_sms=0, gather_rows=None, units=None):
     """-> (dgu [S,2I], act_w [S,I], droute partial sums [S, parts] fp32)."""
     S, H = (gather_rows.numel() if gather_rows is not None else dyperm.shape[0]), dyperm.shape[1]
     I = w_down.shape[2]
@@ -67,7 +86,7 @@ def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, statu
     act_w = torch.empty(S, I, dtype=dyperm.dtype, device=dyperm.device)
     if dyperm.is_cuda:
         parts = torch.empty(S, num_droute_parts(I), dtype=torch.float32, device=dyperm.device)
-        load_ext().gemm_bwd_gradact(dyperm, w_down, preact, row_w, dgu, act_w, parts, mblock_expert, num_mblocks, gather_rows, status,
+        load_ext().gemm_bwd_gradact(dyperm, w_down, preact, row_w, dgu, act_w, parts, _lay(mblock_expert, num_mblocks, units), gather_rows, status,
                                     num_sms)
         return dgu, act_w, parts
     if gather_rows is not None:
@@ -77,18 +96,18 @@ def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, statu
     return dgu, act_w, parts
 
 
-def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0):
+def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0, units=None):
     S = dgu.shape[0]
     H = w_gateup.shape[2]
     dx = torch.empty(S, H, dtype=dgu.dtype, device=dgu.device)
     if dgu.is_cuda:
-        load_ext().gemm_bwd_dx(dgu, w_gateup, dx, mblock_expert, num_mblocks, status, num_sms)
+        load_ext().gemm_bwd_dx(dgu, w_gateup, dx, _lay(mblock_expert, num_mblocks, units), status, num_sms)
     else:
         ref_mgroup(dgu, w_gateup, mblock_expert, int(num_mblocks), dx)
     return dx
 
 
-def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0, gather_rows=None, gather_operand=0):
+def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0, gather_rows=None, gather_operand=0, cta_pairs=False):
     """dW[e] = a[seg_e]^T @ b[seg_e]  -> [E, a.shape[1], b.shape[1]] bf16 (zeros for empty experts).
     gather_operand 1 / 2: operand a / b is a row source read through gather_rows."""
     M, N = a.shape[1], b.shape[1]
@@ -97,7 +116,7 @@ def wgrad(a, b, seg_offsets, num_local_experts, status=None, num_sms=0, gather_r
     if S == 0 or a.shape[0] == 0 or b.shape[0] == 0:
         return dw.zero_()
     if a.is_cuda:
-        load_ext().gemm_wgrad(a, b, dw, seg_offsets, gather_rows, gather_operand if gather_rows is not None else 0, status, num_sms)
+        load_ext().gemm_wgrad(a, b, dw, seg_offsets, gather_rows, gather_operand if gather_rows is not None else 0, cta_pairs, status, num_sms)
     else:
         if gather_rows is not None and gather_operand == 1:
             a = _gathered(a, gather_rows)

@@ -143,3 +143,41 @@ def test_gather_modes_match_dense(H, I, counts):
     assert torch.equal(w3, w4)
     torch.cuda.synchronize()
     assert st.tolist()[0] == 0
+
+
+@pytest.mark.parametrize("H,I,counts", CASES + [(512, 512, [128, 256, 0, 384, 129])])
+def test_cta_pair_kernels_match_one_cta(H, I, counts):
+    """cta_group::2 (256x256 tiles over CTA pairs) kernels give bitwise the one-CTA results."""
+    dev = "cuda"
+    torch.manual_seed(4)
+    E = len(counts)
+    S, offs, me, nmb, valid = _layout(counts, dev)
+    units = gemm.make_units(me)
+    x = (torch.randn(S, H, device=dev) * 0.5).to(torch.bfloat16) * valid[:, None]
+    wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
+    row_w = torch.rand(S, device=dev) * valid
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    a1, p1 = gemm.fwd_gateup(x, wgu, row_w, me, nmb, st)
+    a2, p2 = gemm.fwd_gateup(x, wgu, row_w, me, nmb, st, units=units)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0, st.tolist()
+    assert torch.equal(p1, p2) and torch.equal(a1, a2)
+    y1 = gemm.fwd_down(a1, wd, me, nmb, st)
+    y2 = gemm.fwd_down(a1, wd, me, nmb, st, units=units)
+    assert torch.equal(y1, y2)
+    d1 = gemm.bwd_gradact(x, wd, p1, row_w, me, nmb, st)
+    d2 = gemm.bwd_gradact(x, wd, p1, row_w, me, nmb, st, units=units)
+    for u, v in zip(d1, d2):
+        assert torch.equal(u, v)
+    x1 = gemm.bwd_dx(d1[0], wgu, me, nmb, st)
+    x2 = gemm.bwd_dx(d1[0], wgu, me, nmb, st, units=units)
+    assert torch.equal(x1, x2)
+    w1 = gemm.wgrad(d1[0], x, offs, E, st)
+    w2 = gemm.wgrad(d1[0], x, offs, E, st, cta_pairs=True)
+    assert torch.equal(w1, w2)
+    w3 = gemm.wgrad(x, d1[1], offs, E, st)
+    w4 = gemm.wgrad(x, d1[1], offs, E, st, cta_pairs=True)
+    assert torch.equal(w3, w4)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0, st.tolist()
