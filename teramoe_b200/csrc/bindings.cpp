@@ -58,6 +58,23 @@ tmoe::MGroupLayout make_layout(const std::vector<torch::Tensor>& t, int S) {
     return lay;
 }
 
+// Python passes the push target as ([arena_ptrs int64, slot_tk, slot_row, recv_row_base], landing_off).
+bool make_push(const c10::optional<std::vector<torch::Tensor>>& t, int64_t landing_off, tmoe::PushTarget& p) {
+    if (!t.has_value()) return false;
+    TORCH_CHECK(t->size() == 4, "push target must be [arena_ptrs, slot_tk, slot_row, recv_row_base]");
+    const auto& v = *t;
+    TORCH_CHECK(v[0].is_cuda() && v[0].scalar_type() == torch::kInt64 && v[0].is_contiguous(), "arena_ptrs must be int64 CUDA");
+    check_i32(v[1], "slot_tk"); check_i32(v[2], "slot_row"); check_i32(v[3], "recv_row_base");
+    p.arena_ptrs = reinterpret_cast<const uint64_t*>(v[0].data_ptr<int64_t>());
+    p.landing_off = (uint64_t)landing_off;
+    p.slot_tk = v[1].data_ptr<int>();
+    p.slot_row = v[2].data_ptr<int>();
+    p.recv_row_base = v[3].data_ptr<int>();
+    p.num_ranks = (int)v[0].numel();
+    TORCH_CHECK(v[3].numel() == p.num_ranks + 1, "recv_row_base must have ranks + 1 entries");
+    return true;
+}
+
 // ---- grouped GEMMs ------------------------------------------------------------------------------
 void gemm_fwd_gateup(torch::Tensor xperm, torch::Tensor w_gateup, torch::Tensor act, torch::Tensor preact, torch::Tensor row_w,
                      std::vector<torch::Tensor> layout, c10::optional<torch::Tensor> gather_rows,
@@ -76,15 +93,18 @@ void gemm_fwd_gateup(torch::Tensor xperm, torch::Tensor w_gateup, torch::Tensor 
                                         (int)xperm.size(0), status_ptr(status), (int)num_sms, cur_stream()));
 }
 
-void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, torch::Tensor y, std::vector<torch::Tensor> layout,
-                   c10::optional<torch::Tensor> status, int64_t num_sms) {
+void gemm_fwd_down(torch::Tensor act, torch::Tensor w_down, c10::optional<torch::Tensor> y_opt, std::vector<torch::Tensor> layout,
+                   c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<std::vector<torch::Tensor>> push, int64_t landing_off) {
+    tmoe::PushTarget pt;
+    const bool has_push = make_push(push, landing_off, pt);
+    TORCH_CHECK(has_push || y_opt.has_value(), "gemm_fwd_down: need y or a push target");
+    torch::Tensor y = y_opt.has_value() ? *y_opt : act;
     check_bf16(act, "act"); check_bf16(w_down, "w_down"); check_bf16(y, "y");
-    
     const int S = act.size(0), I = act.size(1), E = w_down.size(0), H = w_down.size(1);
-    TORCH_CHECK(S % 128 == 0 && w_down.size(2) == I && y.size(0) == S && y.size(1) == H,
-                "gemm_fwd_down: shape mismatch");
+    TORCH_CHECK(S % 128 == 0 && w_down.size(2) == I && (has_push || (y.size(0) == S && y.size(1) == H)), "gemm_fwd_down: shape mismatch");
+    if (has_push) TORCH_CHECK(push->at(1).numel() >= S && push->at(2).numel() >= S, "push tables too small");
     c10::cuda::CUDAGuard guard(act.device());
-    TM_CHECK_CUDA(tmoe::gemm_fwd_down(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+    TM_CHECK_CUDA(tmoe::gemm_fwd_down(act.data_ptr(), w_down.data_ptr(), y.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream(), has_push ? &pt : nullptr));
 }
 
 void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor preact, torch::Tensor row_w, torch::Tensor dgu,
@@ -107,15 +127,20 @@ void gemm_bwd_gradact(torch::Tensor dyperm, torch::Tensor w_down, torch::Tensor 
                                          (int)num_sms, cur_stream()));
 }
 
-void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, torch::Tensor dxperm, std::vector<torch::Tensor> layout,
-                 c10::optional<torch::Tensor> status, int64_t num_sms) {
+void gemm_bwd_dx(torch::Tensor dgu, torch::Tensor w_gateup, c10::optional<torch::Tensor> dx_opt, std::vector<torch::Tensor> layout,
+                 c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<std::vector<torch::Tensor>> push, int64_t landing_off) {
+    tmoe::PushTarget pt;
+    const bool has_push = make_push(push, landing_off, pt);
+    TORCH_CHECK(has_push || dx_opt.has_value(), "gemm_bwd_dx: need dxperm or a push target");
+    torch::Tensor dxperm = dx_opt.has_value() ? *dx_opt : dgu;
     check_bf16(dgu, "dgu"); check_bf16(w_gateup, "w_gateup"); check_bf16(dxperm, "dxperm");
     
     const int S = dgu.size(0), I = dgu.size(1) / 2, E = w_gateup.size(0), H = w_gateup.size(2);
-    TORCH_CHECK(S % 128 == 0 && w_gateup.size(1) == 2 * I && dxperm.size(0) == S && dxperm.size(1) == H,
+    TORCH_CHECK(S % 128 == 0 && w_gateup.size(1) == 2 * I && (has_push || (dxperm.size(0) == S && dxperm.size(1) == H)),
                 "gemm_bwd_dx: shape mismatch");
+    if (has_push) TORCH_CHECK(push->at(1).numel() >= S && push->at(2).numel() >= S, "push tables too small");
     c10::cuda::CUDAGuard guard(dgu.device());
-    TM_CHECK_CUDA(tmoe::gemm_bwd_dx(dgu.data_ptr(), w_gateup.data_ptr(), dxperm.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream()));
+    TM_CHECK_CUDA(tmoe::gemm_bwd_dx(dgu.data_ptr(), w_gateup.data_ptr(), dxperm.data_ptr(), make_layout(layout, S), H, I, E, status_ptr(status), (int)num_sms, cur_stream(), has_push ? &pt : nullptr));
 }
 
 void gemm_wgrad(torch::Tensor a, torch::Tensor b, torch::Tensor dw, torch::Tensor seg_offsets, c10::optional<torch::Tensor> gather_rows,

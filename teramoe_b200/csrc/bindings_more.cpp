@@ -163,6 +163,24 @@ void combine_reduce(torch::Tensor landing, torch::Tensor land_off, torch::Tensor
                                        (int)out.size(0), (int)out.size(1), cur_stream()));
 }
 
+void combine_reduce_slots(torch::Tensor landing, torch::Tensor topk_idx, int64_t E, torch::Tensor out) {
+    const TopK tk = topk(topk_idx);
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == tk.T && landing.size(0) >= (int64_t)tk.T * tk.K && landing.size(1) == out.size(1),
+                "combine_reduce_slots: shape mismatch");
+    c10::cuda::CUDAGuard guard(out.device());
+    TM_CHECK_CUDA(tmoe::combine_reduce_slots(bf16(landing, "landing"), tk.ptr, tk.is64, bf16(out, "out"), tk.T, tk.K, (int)out.size(1), (int)E,
+                                             cur_stream()));
+}
+
+void droute_push(torch::Tensor droute_part, torch::Tensor slot_tk, torch::Tensor slot_row, torch::Tensor recv_row_base, int64_t S,
+                 torch::Tensor arena_ptrs, int64_t gtw_off) {
+    TORCH_CHECK(droute_part.dim() == 2 && droute_part.size(0) >= S && slot_tk.numel() >= S && slot_row.numel() >= S, "droute_push: shapes");
+    c10::cuda::CUDAGuard guard(droute_part.device());
+    TM_CHECK_CUDA(tmoe::droute_push(f32(droute_part, "droute_part"), (int)droute_part.size(1), i32(slot_tk, "slot_tk"),
+                                    i32(slot_row, "slot_row"), i32(recv_row_base, "recv_row_base"), (int)S, (int)arena_ptrs.numel(),
+                                    u64(arena_ptrs, "arena_ptrs"), (uint64_t)gtw_off, cur_stream()));
+}
+
 torch::Tensor numerics_check(torch::Tensor a, torch::Tensor b) {
     TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.is_contiguous() && b.is_contiguous() && a.numel() == b.numel() &&
                 a.scalar_type() == b.scalar_type(), "numerics_check: two contiguous CUDA tensors of one dtype and size");
@@ -201,6 +219,8 @@ void register_more(pybind11::module_& m) {
     m.def("expand_rows", &expand_rows);
     m.def("combine_push", &combine_push);
     m.def("combine_reduce", &combine_reduce);
+    m.def("combine_reduce_slots", &combine_reduce_slots);
+    m.def("droute_push", &droute_push);
     m.def("numerics_check", &numerics_check);
 
     py::class_<tmoe::SymmetricArena>(m, "SymmetricArena")

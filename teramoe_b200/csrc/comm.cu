@@ -189,6 +189,45 @@ combine_reduce_kernel(const __nv_bfloat16* landing, const int* land_off, const i
     }
 }
 
+// Per-(token,k) landing table [T*K, H]: out[t] = fp32 sum over the token's valid entries, one rounding.
+__global__ void __launch_bounds__(256)
+combine_reduce_slots_kernel(const __nv_bfloat16* landing, const void* topk_idx, int is64, __nv_bfloat16* out, int T, int K, int H,
+                            int E) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    const int nvec = H / 8;
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps_per_grid) {
+        int64_t e = -1;
+        if (lane < K) e = load_topk(topk_idx, is64, (long)t * K + lane);
+        const uint32_t valid = __ballot_sync(0xffffffffu, e >= 0 && e < E);
+        int4* dst = reinterpret_cast<int4*>(out + (long)t * H);
+        for (int i = lane; i < nvec; i += 32) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (uint32_t m = valid; m != 0; m &= m - 1) {
+                const int k = __ffs(m) - 1;
+                accum_bf16x8(acc, ld_nc_v4(reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H) + i));
+            }
+            dst[i] = pack_bf16x8(acc);
+        }
+    }
+}
+
+// Route-weight gradients of every slot go home: gtw[slot_tk] on the source rank = sum of the partials.
+__global__ void __launch_bounds__(256)
+droute_push_kernel(const float* droute_part, int n_parts, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S,
+                   int N, const uint64_t* arena_ptrs, uint64_t gtw_off) {
+    for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < S; s += gridDim.x * blockDim.x) {
+        const int tk = slot_tk[s];
+        if (tk < 0) continue;
+        const int rr = slot_row[s];
+        int src = 0;
+        while (src + 1 < N && rr >= recv_row_base[src + 1]) ++src;
+        float v = 0.f;
+        for (int p = 0; p < n_parts; ++p) v += droute_part[(long)s * n_parts + p];
+        reinterpret_cast<float*>(arena_ptrs[src] + gtw_off)[tk] = v;
+    }
+}
+
 // out[0] = max |a-b| ; out[1..5] = sum ab, sum a^2, sum b^2, sum (a+1)(b+1), sum (a+1)^2 + (b+1)^2
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -262,6 +301,24 @@ cudaError_t combine_reduce(const void* landing, const int* land_off, const int* 
     if (T == 0) return cudaSuccess;
     combine_reduce_kernel<<<grid_for_warps(T, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(landing), land_off, ndst,
                                                                       static_cast<__nv_bfloat16*>(out), T, H);
+    return cudaGetLastError();
+}
+
+cudaError_t combine_reduce_slots(const void* landing, const void* topk_idx, int is64, void* out, int T, int K, int H, int E,
+                                 cudaStream_t stream) {
+    if (T == 0) return cudaSuccess;
+    if (K > 32 || H % 8 != 0) return cudaErrorInvalidValue;
+    combine_reduce_slots_kernel<<<grid_for_warps(T, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(landing), topk_idx, is64,
+                                                                            static_cast<__nv_bfloat16*>(out), T, K, H, E);
+    return cudaGetLastError();
+}
+
+cudaError_t droute_push(const float* droute_part, int n_parts, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S,
+                        int N, const uint64_t* arena_ptrs, uint64_t gtw_off, cudaStream_t stream) {
+    if (S == 0) return cudaSuccess;
+    int blocks = (S + 255) / 256;
+    if (blocks > 1184) blocks = 1184;
+    droute_push_kernel<<<blocks, 256, 0, stream>>>(droute_part, n_parts, slot_tk, slot_row, recv_row_base, S, N, arena_ptrs, gtw_off);
     return cudaGetLastError();
 }
 

@@ -257,6 +257,15 @@ cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs&
     return cudaGetLastError();
 }
 
+void set_push(GemmArgs& g, const PushTarget& p) {
+    g.push_ptrs = reinterpret_cast<const unsigned long long*>(p.arena_ptrs);
+    g.push_off = p.landing_off;
+    g.slot_tk = p.slot_tk;
+    g.slot_row = p.slot_row;
+    g.recv_row_base = p.recv_row_base;
+    g.num_ranks = p.num_ranks;
+}
+
 }  // namespace
 
 int gemm_num_droute_parts(int I) { return 2 * ((I + BN - 1) / BN); }
@@ -301,7 +310,7 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
 }
 
 cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const MGroupLayout& lay, int H, int I,
-                          int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+                          int num_local_experts, int* status, int num_sms, cudaStream_t stream, const PushTarget* push) {
     const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if (I % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
@@ -323,6 +332,10 @@ cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const MG
     g.d = static_cast<__nv_bfloat16*>(y);
     g.ldd = H;
     g.status = status;
+    if (push != nullptr) {
+        set_push(g, *push);
+        return launch<false, false, false, kEpiPush, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    }
     if (lay.unit_blk != nullptr) return gemm2_mgroup(1, act, w_down, g, max_mblocks * BM, I, num_local_experts * H, I, num_sms, stream);
     return launch<false, false, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
@@ -371,7 +384,7 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
 }
 
 cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const MGroupLayout& lay, int H, int I,
-                        int num_local_experts, int* status, int num_sms, cudaStream_t stream) {
+                        int num_local_experts, int* status, int num_sms, cudaStream_t stream, const PushTarget* push) {
     const int max_mblocks = lay.max_mblocks;
     if (max_mblocks <= 0) return cudaSuccess;
     if ((2 * I) % BK != 0 || H % 8 != 0) return cudaErrorInvalidValue;
@@ -394,6 +407,10 @@ cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, con
     g.d = static_cast<__nv_bfloat16*>(dxperm);
     g.ldd = H;
     g.status = status;
+    if (push != nullptr) {
+        set_push(g, *push);
+        return launch<false, true, false, kEpiPush, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+    }
     if (lay.unit_blk != nullptr)
         return gemm2_mgroup(3, dgu, w_gateup, g, max_mblocks * BM, 2 * I, num_local_experts * 2 * I, H, num_sms, stream);
     return launch<false, true, false, kEpiStore, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);

@@ -14,6 +14,18 @@
 
 namespace tmoe {
 
+// Destination of the "push" epilogues: output row s (a slot) is stored straight into the landing table
+// of the rank that owns the token, at row slot_tk[s] (= t*K+k at the source), with peer stores over
+// NVLink issued from the GEMM epilogue.  Pad rows (slot_tk < 0) are skipped.
+struct PushTarget {
+    const uint64_t* arena_ptrs = nullptr;  // device [ranks]: base address of every rank's symmetric arena
+    uint64_t landing_off = 0;              // byte offset of the [T*K, H] landing table inside the arena
+    const int* slot_tk = nullptr;          // device [slots]
+    const int* slot_row = nullptr;         // device [slots]
+    const int* recv_row_base = nullptr;    // device [ranks + 1]
+    int num_ranks = 1;
+};
+
 // Returns cudaSuccess or the launch / tensor-map error.  `status` is a 4-int device block that the
 // kernels fill when a bounded wait runs out (see ptx.cuh); may be nullptr.
 //
@@ -37,8 +49,10 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
                             cudaStream_t stream);
 
 // y[S,H] = act[S,I] . W_down[e]^T          (W_down [E,H,I])
+// With `push` the rows are not written to y (may be null) but pushed to their source ranks (combine fused into
+// the GEMM epilogue).
 cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const MGroupLayout& lay, int H, int I,
-                          int num_local_experts, int* status, int num_sms, cudaStream_t stream);
+                          int num_local_experts, int* status, int num_sms, cudaStream_t stream, const PushTarget* push = nullptr);
 
 // ga = dy[S,H] . W_down[e]  (fp32, never stored), then fused dSwiGLU with the saved preact:
 //   dgu[S,2I] interleaved (d_gate,d_up), act_w[S,I] = row_w * silu(g) * u (operand of dW_down),
@@ -49,7 +63,7 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
 
 // dxperm[S,H] = dgu[S,2I] . W_gateup[e]
 cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, const MGroupLayout& lay, int H, int I,
-                        int num_local_experts, int* status, int num_sms, cudaStream_t stream);
+                        int num_local_experts, int* status, int num_sms, cudaStream_t stream, const PushTarget* push = nullptr);
 
 // dW[e] [M,N] = A[seg_e, M]^T . B[seg_e, N]  for every local expert, seg_e = rows
 // [seg_offsets[e], seg_offsets[e+1]) of slot space (multiples of 128).  Empty segments give zeros.

@@ -6,11 +6,11 @@
 // both CTAs' tensor memory (128 accumulator rows each).  Per CTA a pipeline stage is 32 KB instead
 // of 48 KB, so six stages fit and the L2 -> SM traffic per FLOP drops by a third.
 //
-// Status: numerically identical (bitwise) to the one-CTA kernels, but measured SLOWER on B200
-// (about 600-780 TFLOP/s against 1200-1430): with the loads disabled the pair's UMMAs alone issue at
-// 1900 TFLOP/s, with the UMMAs disabled the loads alone run at the same low rate as the full kernel,
-// so the limit is the operand-load path of the pair, not the tensor cores.  The cause is not found
-// yet; the engine therefore uses these kernels only when TERAMOE_CTA_PAIRS=1.  Every CTA loads
+// Measured on B200 (H=7168, I=2048, 32 experts x 2048 rows): 1437 / 1523 / 1373 / 1545 TFLOP/s for
+// gate_up / down / grad_act / dX and 1259 / 1268 for the two weight gradients, against 1359 / 1297 /
+// 1171 / 1396 / 987 / 1004 for the one-CTA kernels; results are bitwise identical.  Remote mbarrier
+// arrives must use CTA-scope release (ptx.cuh mbar_arrive_cluster): with a cluster-scope release
+// every arrive paid a fence and the same kernels ran at 600-780 TFLOP/s.  Every CTA loads
 // its operands itself with plain (non-multicast) TMA loads from local memory; only barrier arrivals
 // cross the pair (tcgen05.commit to both CTAs, remote mbarrier arrives).
 //

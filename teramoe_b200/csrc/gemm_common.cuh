@@ -27,7 +27,7 @@ constexpr int kTmemCols = 512;
 constexpr int kSuperM = 16;  // m-blocks per L2 super-group
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-enum Epilogue : int { kEpiStore = 0, kEpiSwiGLU = 1, kEpiDSwiGLU = 2 };
+enum Epilogue : int { kEpiStore = 0, kEpiSwiGLU = 1, kEpiDSwiGLU = 2, kEpiPush = 3 };
 
 struct GemmArgs {
     int n_total;                 // columns of D per group
@@ -49,6 +49,14 @@ struct GemmArgs {
     const int* unit_blk;         // CTA-pair kernels: [max_units + 1] first m-block of each unit (last = block count)
     const int* num_units_dev;    // CTA-pair kernels: device-side live unit count
     int max_units;               // CTA-pair kernels: bound on units (M-grouped); unused in weight-gradient mode
+    // kEpiPush: every output row goes straight to the rank that owns the token (peer store over NVLink):
+    // row s lands at push_ptrs[source rank of s] + push_off + slot_tk[s] * ldd elements.
+    const unsigned long long* push_ptrs;  // [ranks] base address of every rank's symmetric arena
+    unsigned long long push_off;          // byte offset of the per-(token,k) landing table inside the arena
+    const int* slot_tk;                   // [rows] t*K+k of the row's entry at its source (-1 = pad row)
+    const int* slot_row;                  // [rows] receive row (locates the source rank through recv_row_base)
+    const int* recv_row_base;             // [ranks+1]
+    int num_ranks;
     const int* gather_rows;      // GATHER modes: source row of each slot-space row (-1 = zero row)
     float* droute_part;          // bwd grad_act: [rows, n_parts]
     int n_parts;
@@ -105,89 +113,101 @@ __device__ __forceinline__ void store_bf16x8(__nv_bfloat16* p, const uint32_t* a
 template <int EPI>
 __device__ __forceinline__ void epilogue_thread(const GemmArgs& g, uint32_t taddr0, long row, bool row_ok, int n0, int part_idx,
                                                 bool zero_tile) {
-                float w = 0.f;
-                if constexpr (EPI != kEpiStore) w = g.row_w[row];
-                float droute = 0.f;
-    #pragma unroll 1
-                for (int c = 0; c < (BN / 2) / 32; ++c) {
-                    uint32_t acc[32];
-                    tmem_ld_x32(taddr0 + (uint32_t)(c * 32), acc);
-                    tmem_ld_wait();
-                    const int col = n0 + c * 32;
-                    if (zero_tile) {
-    #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[i] = 0u;
+    float w = 0.f;
+    if constexpr (EPI == kEpiSwiGLU || EPI == kEpiDSwiGLU) w = g.row_w[row];
+    __nv_bfloat16* push_dst = nullptr;
+    if constexpr (EPI == kEpiPush) {
+        const int tk = row_ok ? g.slot_tk[row] : -1;
+        if (tk < 0) {
+            row_ok = false;
+        } else {
+            const int rr = g.slot_row[row];
+            int src = 0;
+            while (src + 1 < g.num_ranks && rr >= g.recv_row_base[src + 1]) ++src;
+            push_dst = reinterpret_cast<__nv_bfloat16*>(g.push_ptrs[src] + g.push_off) + (long)tk * g.ldd;
+        }
+    }
+    float droute = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < (BN / 2) / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_x32(taddr0 + (uint32_t)(c * 32), acc);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (zero_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0u;
+        }
+        if constexpr (EPI == kEpiStore || EPI == kEpiPush) {
+            if (row_ok) {
+                __nv_bfloat16* dst = (EPI == kEpiPush ? push_dst : g.d + row * g.ldd) + col;
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    if (col + v * 8 + 8 <= g.n_total) store_bf16x8(dst + v * 8, acc + v * 8);
+            }
+        } else if constexpr (EPI == kEpiSwiGLU) {
+            // accumulator columns (2j, 2j+1) = (gate_j, up_j); n_total = 2I
+            if (col < g.n_total) {
+                store_bf16x8(g.aux + row * g.ld_aux + col, acc);
+                store_bf16x8(g.aux + row * g.ld_aux + col + 8, acc + 8);
+                store_bf16x8(g.aux + row * g.ld_aux + col + 16, acc + 16);
+                store_bf16x8(g.aux + row * g.ld_aux + col + 24, acc + 24);
+                uint32_t o[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    float a2[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float gt = __uint_as_float(acc[4 * p + 2 * e]);
+                        const float up = __uint_as_float(acc[4 * p + 2 * e + 1]);
+                        a2[e] = gt / (1.f + expf(-gt)) * up * w;
                     }
-                    if constexpr (EPI == kEpiStore) {
-                        if (row_ok) {
-                            __nv_bfloat16* dst = g.d + row * g.ldd + col;
-    #pragma unroll
-                            for (int v = 0; v < 4; ++v)
-                                if (col + v * 8 + 8 <= g.n_total) store_bf16x8(dst + v * 8, acc + v * 8);
-                        }
-                    } else if constexpr (EPI == kEpiSwiGLU) {
-                        // accumulator columns (2j, 2j+1) = (gate_j, up_j); n_total = 2I
-                        if (col < g.n_total) {
-                            store_bf16x8(g.aux + row * g.ld_aux + col, acc);
-                            store_bf16x8(g.aux + row * g.ld_aux + col + 8, acc + 8);
-                            store_bf16x8(g.aux + row * g.ld_aux + col + 16, acc + 16);
-                            store_bf16x8(g.aux + row * g.ld_aux + col + 24, acc + 24);
-                            uint32_t o[8];
-    #pragma unroll
-                            for (int p = 0; p < 8; ++p) {
-                                float a2[2];
-    #pragma unroll
-                                for (int e = 0; e < 2; ++e) {
-                                    const float gt = __uint_as_float(acc[4 * p + 2 * e]);
-                                    const float up = __uint_as_float(acc[4 * p + 2 * e + 1]);
-                                    a2[e] = gt / (1.f + expf(-gt)) * up * w;
-                                }
-                                o[p] = pack_bf16x2(a2[0], a2[1]);
-                            }
-                            __nv_bfloat16* dst = g.d + row * g.ldd + (col >> 1);
-                            *reinterpret_cast<int4*>(dst) = make_int4((int)o[0], (int)o[1], (int)o[2], (int)o[3]);
-                            *reinterpret_cast<int4*>(dst + 8) = make_int4((int)o[4], (int)o[5], (int)o[6], (int)o[7]);
-                        }
-                    } else {
-                        // accumulator column j = d act_j; n_total = I.  preact holds (g_j, u_j) at [2j, 2j+1].
-                        if (col < g.n_total) {
-                            const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
-                            uint32_t dgu[32];
-                            uint32_t aw[16];
-    #pragma unroll
-                            for (int v = 0; v < 8; ++v) {
-                                const int4 pv = pp[v];
-                                const uint32_t pr[4] = {(uint32_t)pv.x, (uint32_t)pv.y, (uint32_t)pv.z, (uint32_t)pv.w};
-                                float av[4];
-    #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 gu = unpack_bf16x2(pr[e]);
-                                    const float ga = __uint_as_float(acc[4 * v + e]);
-                                    const float sig = 1.f / (1.f + __expf(-gu.x));
-                                    const float s = gu.x * sig;
-                                    const float a = s * gu.y;
-                                    const float gaw = ga * w;
-                                    const float d_up = s * gaw;
-                                    const float d_gate = (sig - s * sig + s) * gaw * gu.y;
-                                    dgu[4 * v + e] = pack_bf16x2(d_gate, d_up);
-                                    av[e] = a * w;
-                                    droute += ga * a;
-                                }
-                                aw[2 * v] = pack_bf16x2(av[0], av[1]);
-                                aw[2 * v + 1] = pack_bf16x2(av[2], av[3]);
-                            }
-                            int4* dg = reinterpret_cast<int4*>(g.aux + row * g.ld_aux + 2 * col);
-    #pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                dg[v] = make_int4((int)dgu[4 * v], (int)dgu[4 * v + 1], (int)dgu[4 * v + 2], (int)dgu[4 * v + 3]);
-                            int4* da = reinterpret_cast<int4*>(g.d + row * g.ldd + col);
-    #pragma unroll
-                            for (int v = 0; v < 4; ++v)
-                                da[v] = make_int4((int)aw[4 * v], (int)aw[4 * v + 1], (int)aw[4 * v + 2], (int)aw[4 * v + 3]);
-                        }
-                    }
+                    o[p] = pack_bf16x2(a2[0], a2[1]);
                 }
-                if constexpr (EPI == kEpiDSwiGLU) g.droute_part[row * g.n_parts + part_idx] = droute;
+                __nv_bfloat16* dst = g.d + row * g.ldd + (col >> 1);
+                *reinterpret_cast<int4*>(dst) = make_int4((int)o[0], (int)o[1], (int)o[2], (int)o[3]);
+                *reinterpret_cast<int4*>(dst + 8) = make_int4((int)o[4], (int)o[5], (int)o[6], (int)o[7]);
+            }
+        } else {
+            // accumulator column j = d act_j; n_total = I.  preact holds (g_j, u_j) at [2j, 2j+1].
+            if (col < g.n_total) {
+                const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
+                uint32_t dgu[32];
+                uint32_t aw[16];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const int4 pv = pp[v];
+                    const uint32_t pr[4] = {(uint32_t)pv.x, (uint32_t)pv.y, (uint32_t)pv.z, (uint32_t)pv.w};
+                    float av[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 gu = unpack_bf16x2(pr[e]);
+                        const float ga = __uint_as_float(acc[4 * v + e]);
+                        const float sig = 1.f / (1.f + __expf(-gu.x));
+                        const float s = gu.x * sig;
+                        const float a = s * gu.y;
+                        const float gaw = ga * w;
+                        const float d_up = s * gaw;
+                        const float d_gate = (sig - s * sig + s) * gaw * gu.y;
+                        dgu[4 * v + e] = pack_bf16x2(d_gate, d_up);
+                        av[e] = a * w;
+                        droute += ga * a;
+                    }
+                    aw[2 * v] = pack_bf16x2(av[0], av[1]);
+                    aw[2 * v + 1] = pack_bf16x2(av[2], av[3]);
+                }
+                int4* dg = reinterpret_cast<int4*>(g.aux + row * g.ld_aux + 2 * col);
+#pragma unroll
+                for (int v = 0; v < 8; ++v)
+                    dg[v] = make_int4((int)dgu[4 * v], (int)dgu[4 * v + 1], (int)dgu[4 * v + 2], (int)dgu[4 * v + 3]);
+                int4* da = reinterpret_cast<int4*>(g.d + row * g.ldd + col);
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    da[v] = make_int4((int)aw[4 * v], (int)aw[4 * v + 1], (int)aw[4 * v + 2], (int)aw[4 * v + 3]);
+            }
+        }
+    }
+    if constexpr (EPI == kEpiDSwiGLU) g.droute_part[row * g.n_parts + part_idx] = droute;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -220,9 +220,12 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive on an mbarrier of any CTA of the cluster (address from mapa_shared)
+// Arrive on an mbarrier of any CTA of the cluster (address from mapa_shared).  Default semantics
+// (release at CTA scope): the arrivals of this library publish no data of their own (operand bytes are
+// tracked by the TMA transaction count, tensor-memory reads by tcgen05 fences), and a cluster-scope
+// release costs a fence of several hundred cycles per arrive, which throttled the whole pipeline.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_2cta(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");

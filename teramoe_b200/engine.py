@@ -34,9 +34,16 @@ from .parallel.world import EPWorld, _round_up
 # copy per ~70 cycles per SM, which caps the gate_up GEMM at 457 TFLOP/s against 1400 with a dense
 # operand, while the expand pass costs 0.3 ms.  So the expanded copy is the default.
 USE_TMA_GATHER = os.environ.get("TERAMOE_TMA_GATHER", "0") == "1"
-# CTA-pair (tcgen05 cta_group::2, 256x256 tiles) GEMM kernels.  Bitwise equal to the one-CTA kernels
-# but measured slower so far (see csrc/gemm2.cu), hence off unless asked for.
-USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "0") == "1"
+# CTA-pair (tcgen05 cta_group::2, 256x256 tiles) GEMM kernels: bitwise equal to the one-CTA 128x256
+# kernels and 6-27 % faster (csrc/gemm2.cu).  "0" selects the one-CTA kernels.
+USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "1") == "1"
+# Combine fused into the GEMM: the epilogues of the down GEMM (forward) and the dX GEMM (backward) store
+# every output row straight into the landing table of the token's rank (peer stores over NVLink, tile by
+# tile, while the tensor cores work on the next tile).  "0" = separate combine_push kernel.
+# Measured at EP=4 (H=7168, I=2048, top-8): 23.8 ms per step against 19.5 ms with the separate kernel:
+# 64-byte row fragments stored from the epilogue are a poor NVLink payload and stall the epilogue
+# warps, and one row per (token,k) is 1.5x the bytes of one row per (token, rank).  Off by default.
+FUSED_COMBINE = os.environ.get("TERAMOE_FUSED_COMBINE", "0") == "1"
 
 TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw")
 
@@ -85,6 +92,7 @@ class SavedForBackward:
 
 def _arena_geometry(maxima, H: int, K: int):
     rmax, smax, lmax, tmax = [max(int(v), 1) for v in maxima]
+    lmax = max(lmax, tmax * K)      # the fused combine lands one row per (token, k) entry
     sizes = {
         "recv_x": rmax * H * 2, "slot_row": smax * 4, "slot_w": smax * 4, "slot_tk": smax * 4,
         "row_tok": rmax * 4, "row_land": rmax * 4, "row_slots": rmax * K * 4,
@@ -333,12 +341,24 @@ class EPEngine:
             xperm = self.expand(saved_x, h)
             act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del xperm
-        y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
-        del act
-        out, _ = yield from self.combine_gen(h, y, tabs, offs)
-        del y
+        if self.is_cuda and FUSED_COMBINE:
+            gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, push=self._push_target(h, offs))
+            del act
+            yield ("barrier",)
+            out = torch.empty(T, H, dtype=x.dtype, device=x.device)
+            if T > 0:
+                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out)
+        else:
+            y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
+            del act
+            out, _ = yield from self.combine_gen(h, y, tabs, offs)
+            del y
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
+
+    def _push_target(self, h: LayerHandle, offs):
+        w = self.world
+        return ([w.ptr_table(w.data, 0, "data"), h.slot_tk, h.slot_row, h.recv_row_base], offs["landing"])
 
     def backward_gen(self, saved: SavedForBackward, grad_out, W_gateup, W_down, impl=None, num_sms=0):
         w = self.world
@@ -359,13 +379,30 @@ class EPEngine:
             dyperm = self.expand(tabs["recv_x"], h)
             dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
                                                  units=units)
-            dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
+            fused = self.is_cuda and FUSED_COMBINE
+            if fused:
+                dxperm = None
+                gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, push=self._push_target(h, offs))
+                if h.slots > 0:
+                    self.ext.droute_push(parts, h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"), offs["gtw"])
+            else:
+                dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del dyperm
             xperm = self.expand(saved.saved_x, h)
             dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del xperm
         del dgu, act_w
+        if dxperm is None and self.is_cuda and FUSED_COMBINE and not USE_TMA_GATHER:
+            # weight gradients were enqueued after the push so they overlap the other ranks' pushes
+            yield ("barrier",)
+            T, K = h.T, h.K
+            dx = torch.empty(T, h.H, dtype=grad_out.dtype, device=grad_out.device)
+            if T > 0:
+                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, dx)
+            valid = (h.topk_idx >= 0) & (h.topk_idx < h.E)
+            gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
+            return dx, gtw, dW_gateup, dW_down
         dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
         return dx, gtw, dW_gateup, dW_down
 

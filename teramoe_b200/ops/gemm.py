@@ -67,12 +67,17 @@ def fwd_gateup(xperm, w_gateup, row_w, mblock_expert, num_mblocks, status=None, 
     return act, preact
 
 
-def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0, units=None):
+def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0, units=None, push=None):
+    """y[S,H] = act @ W_down[e]^T.  With push = ([arena_ptrs, slot_tk, slot_row, recv_row_base], landing_off) the rows
+    are stored straight into their source ranks' landing tables by the GEMM epilogue and None is returned."""
     S, I = act.shape
     H = w_down.shape[1]
+    if push is not None:
+        load_ext().gemm_fwd_down(act, w_down, None, _lay(mblock_expert, num_mblocks, None), status, num_sms, push[0], push[1])
+        return None
     y = torch.empty(S, H, dtype=act.dtype, device=act.device)
     if act.is_cuda:
-        load_ext().gemm_fwd_down(act, w_down, y, _lay(mblock_expert, num_mblocks, units), status, num_sms)
+        load_ext().gemm_fwd_down(act, w_down, y, _lay(mblock_expert, num_mblocks, units), status, num_sms, None, 0)
     else:
         ref_mgroup(act, w_down.transpose(1, 2), mblock_expert, int(num_mblocks), y)
     return y
@@ -96,12 +101,15 @@ def bwd_gradact(dyperm, w_down, preact, row_w, mblock_expert, num_mblocks, statu
     return dgu, act_w, parts
 
 
-def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0, units=None):
+def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0, units=None, push=None):
     S = dgu.shape[0]
     H = w_gateup.shape[2]
+    if push is not None:
+        load_ext().gemm_bwd_dx(dgu, w_gateup, None, _lay(mblock_expert, num_mblocks, None), status, num_sms, push[0], push[1])
+        return None
     dx = torch.empty(S, H, dtype=dgu.dtype, device=dgu.device)
     if dgu.is_cuda:
-        load_ext().gemm_bwd_dx(dgu, w_gateup, dx, _lay(mblock_expert, num_mblocks, units), status, num_sms)
+        load_ext().gemm_bwd_dx(dgu, w_gateup, dx, _lay(mblock_expert, num_mblocks, units), status, num_sms, None, 0)
     else:
         ref_mgroup(dgu, w_gateup, mblock_expert, int(num_mblocks), dx)
     return dx
