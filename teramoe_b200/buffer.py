@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from .config import Config, topk_idx_t
 from .engine import EPEngine, LayerHandle
+from .low_latency import LowLatencyMixin
 from .parallel.world import EPWorld
 from .utils.events import EventHandle, EventOverlap
 from .utils.nvlink import check_nvlink_connections
@@ -53,7 +54,7 @@ class _TeraMoEFunction(torch.autograd.Function):
         return None, dx, None, gtw, dWgu, dWd, None, None, None
 
 
-class Buffer:
+class Buffer(LowLatencyMixin):
     """Expert-parallel communication + fused MoE layer on one NVSwitch node."""
 
     num_sms: int = 20

@@ -163,13 +163,22 @@ void combine_reduce(torch::Tensor landing, torch::Tensor land_off, torch::Tensor
                                        (int)out.size(0), (int)out.size(1), cur_stream()));
 }
 
-void combine_reduce_slots(torch::Tensor landing, torch::Tensor topk_idx, int64_t E, torch::Tensor out) {
+void slot_rows_push(torch::Tensor y, torch::Tensor slot_tk, torch::Tensor slot_row, torch::Tensor recv_row_base, int64_t S,
+                    torch::Tensor arena_ptrs, int64_t landing_off) {
+    TORCH_CHECK(y.dim() == 2 && y.size(0) >= S && slot_tk.numel() >= S && slot_row.numel() >= S, "slot_rows_push: shapes");
+    c10::cuda::CUDAGuard guard(y.device());
+    TM_CHECK_CUDA(tmoe::slot_rows_push(bf16(y, "y"), i32(slot_tk, "slot_tk"), i32(slot_row, "slot_row"), i32(recv_row_base, "recv_row_base"),
+                                       (int)S, (int)y.size(1), (int)arena_ptrs.numel(), u64(arena_ptrs, "arena_ptrs"), (uint64_t)landing_off,
+                                       cur_stream()));
+}
+
+void combine_reduce_slots(torch::Tensor landing, torch::Tensor topk_idx, int64_t E, torch::Tensor out, c10::optional<torch::Tensor> weights) {
     const TopK tk = topk(topk_idx);
     TORCH_CHECK(out.dim() == 2 && out.size(0) == tk.T && landing.size(0) >= (int64_t)tk.T * tk.K && landing.size(1) == out.size(1),
                 "combine_reduce_slots: shape mismatch");
     c10::cuda::CUDAGuard guard(out.device());
     TM_CHECK_CUDA(tmoe::combine_reduce_slots(bf16(landing, "landing"), tk.ptr, tk.is64, bf16(out, "out"), tk.T, tk.K, (int)out.size(1), (int)E,
-                                             cur_stream()));
+                                             weights.has_value() ? f32(*weights, "weights") : nullptr, cur_stream()));
 }
 
 void droute_push(torch::Tensor droute_part, torch::Tensor slot_tk, torch::Tensor slot_row, torch::Tensor recv_row_base, int64_t S,
@@ -220,6 +229,7 @@ void register_more(pybind11::module_& m) {
     m.def("combine_push", &combine_push);
     m.def("combine_reduce", &combine_reduce);
     m.def("combine_reduce_slots", &combine_reduce_slots);
+    m.def("slot_rows_push", &slot_rows_push);
     m.def("droute_push", &droute_push);
     m.def("numerics_check", &numerics_check);
 

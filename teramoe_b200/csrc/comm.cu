@@ -189,10 +189,30 @@ combine_reduce_kernel(const __nv_bfloat16* landing, const int* land_off, const i
     }
 }
 
-// Per-(token,k) landing table [T*K, H]: out[t] = fp32 sum over the token's valid entries, one rounding.
+// One row per slot goes to the rank that owns the token: landing[slot_tk[s]] on the source of slot s.
+__global__ void __launch_bounds__(256)
+slot_rows_push_kernel(const __nv_bfloat16* y, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S, int H, int N,
+                      const uint64_t* arena_ptrs, uint64_t landing_off) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    const int nvec = H / 8;
+    for (int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < S; s += warps_per_grid) {
+        const int tk = slot_tk[s];
+        if (tk < 0) continue;
+        const int rr = slot_row[s];
+        int src = 0;
+        while (src + 1 < N && rr >= recv_row_base[src + 1]) ++src;
+        int4* dst = reinterpret_cast<int4*>(arena_ptrs[src] + landing_off + (uint64_t)tk * H * 2);
+        const int4* p = reinterpret_cast<const int4*>(y + (long)s * H);
+        for (int i = lane; i < nvec; i += 32) st_na_v4(dst + i, p[i]);
+    }
+}
+
+// Per-(token,k) landing table [T*K, H]: out[t] = fp32 sum over the token's valid entries (optionally
+// weighted by w[t,k]), one rounding.
 __global__ void __launch_bounds__(256)
 combine_reduce_slots_kernel(const __nv_bfloat16* landing, const void* topk_idx, int is64, __nv_bfloat16* out, int T, int K, int H,
-                            int E) {
+                            int E, const float* weights) {
     const int lane = threadIdx.x & 31;
     const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
     const int nvec = H / 8;
@@ -205,7 +225,16 @@ combine_reduce_slots_kernel(const __nv_bfloat16* landing, const void* topk_idx, 
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (uint32_t m = valid; m != 0; m &= m - 1) {
                 const int k = __ffs(m) - 1;
-                accum_bf16x8(acc, ld_nc_v4(reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H) + i));
+                const int4 v = ld_nc_v4(reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H) + i);
+                if (weights == nullptr) {
+                    accum_bf16x8(acc, v);
+                } else {
+                    float one[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    accum_bf16x8(one, v);
+                    const float wk = weights[(long)t * K + k];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] += wk * one[j];
+                }
             }
             dst[i] = pack_bf16x8(acc);
         }
@@ -304,12 +333,21 @@ cudaError_t combine_reduce(const void* landing, const int* land_off, const int* 
     return cudaGetLastError();
 }
 
+cudaError_t slot_rows_push(const void* y, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S, int H, int N,
+                           const uint64_t* arena_ptrs, uint64_t landing_off, cudaStream_t stream) {
+    if (S == 0) return cudaSuccess;
+    if (H % 8 != 0) return cudaErrorInvalidValue;
+    slot_rows_push_kernel<<<grid_for_warps(S, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), slot_tk, slot_row,
+                                                                      recv_row_base, S, H, N, arena_ptrs, landing_off);
+    return cudaGetLastError();
+}
+
 cudaError_t combine_reduce_slots(const void* landing, const void* topk_idx, int is64, void* out, int T, int K, int H, int E,
-                                 cudaStream_t stream) {
+                                 const float* weights, cudaStream_t stream) {
     if (T == 0) return cudaSuccess;
     if (K > 32 || H % 8 != 0) return cudaErrorInvalidValue;
     combine_reduce_slots_kernel<<<grid_for_warps(T, 256), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(landing), topk_idx, is64,
-                                                                            static_cast<__nv_bfloat16*>(out), T, K, H, E);
+                                                                            static_cast<__nv_bfloat16*>(out), T, K, H, E, weights);
     return cudaGetLastError();
 }
 

@@ -35,7 +35,9 @@ cudaError_t combine_reduce(const void* landing, const int* land_off, const int* 
 // Fused-combine path: the down / dX GEMM epilogues store one row per (token,k) entry into the landing
 // table [T*K, H] of the token's rank; the reduce sums a token's valid entries.
 cudaError_t combine_reduce_slots(const void* landing, const void* topk_idx, int is64, void* out, int T, int K, int H, int E,
-                                 cudaStream_t stream);
+                                 const float* weights /* optional [T,K] */, cudaStream_t stream);
+cudaError_t slot_rows_push(const void* y, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S, int H, int N,
+                           const uint64_t* arena_ptrs, uint64_t landing_off, cudaStream_t stream);
 cudaError_t droute_push(const float* droute_part, int n_parts, const int* slot_tk, const int* slot_row, const int* recv_row_base, int S,
                         int N, const uint64_t* arena_ptrs, uint64_t gtw_off, cudaStream_t stream);
 

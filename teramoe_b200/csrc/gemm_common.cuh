@@ -130,10 +130,19 @@ __device__ __forceinline__ void epilogue_thread(const GemmArgs& g, uint32_t tadd
     float droute = 0.f;
 #pragma unroll 1
     for (int c = 0; c < (BN / 2) / 32; ++c) {
+        const int col = n0 + c * 32;
+        int4 pre[8];
+        if constexpr (EPI == kEpiDSwiGLU) {
+            // issue the pre-activation loads before the tensor-memory load so their latencies overlap
+            if (col < g.n_total) {
+                const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) pre[v] = ld_nc_v4(pp + v);
+            }
+        }
         uint32_t acc[32];
         tmem_ld_x32(taddr0 + (uint32_t)(c * 32), acc);
         tmem_ld_wait();
-        const int col = n0 + c * 32;
         if (zero_tile) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0u;
@@ -160,7 +169,7 @@ __device__ __forceinline__ void epilogue_thread(const GemmArgs& g, uint32_t tadd
                     for (int e = 0; e < 2; ++e) {
                         const float gt = __uint_as_float(acc[4 * p + 2 * e]);
                         const float up = __uint_as_float(acc[4 * p + 2 * e + 1]);
-                        a2[e] = gt / (1.f + expf(-gt)) * up * w;
+                        a2[e] = __fdividef(gt, 1.f + __expf(-gt)) * up * w;
                     }
                     o[p] = pack_bf16x2(a2[0], a2[1]);
                 }
@@ -171,19 +180,18 @@ __device__ __forceinline__ void epilogue_thread(const GemmArgs& g, uint32_t tadd
         } else {
             // accumulator column j = d act_j; n_total = I.  preact holds (g_j, u_j) at [2j, 2j+1].
             if (col < g.n_total) {
-                const int4* pp = reinterpret_cast<const int4*>(g.preact + row * (2l * g.n_total) + 2 * col);
                 uint32_t dgu[32];
                 uint32_t aw[16];
 #pragma unroll
                 for (int v = 0; v < 8; ++v) {
-                    const int4 pv = pp[v];
+                    const int4 pv = pre[v];
                     const uint32_t pr[4] = {(uint32_t)pv.x, (uint32_t)pv.y, (uint32_t)pv.z, (uint32_t)pv.w};
                     float av[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float2 gu = unpack_bf16x2(pr[e]);
                         const float ga = __uint_as_float(acc[4 * v + e]);
-                        const float sig = 1.f / (1.f + __expf(-gu.x));
+                        const float sig = __fdividef(1.f, 1.f + __expf(-gu.x));
                         const float s = gu.x * sig;
                         const float a = s * gu.y;
                         const float gaw = ga * w;

@@ -318,6 +318,43 @@ class EPEngine:
         yield ("barrier",)
         return self._combine_reduce(hh, tabs, x.dtype, dev, recv_topk_weights is not None)
 
+    def slots_combine_gen(self, h: LayerHandle, y: torch.Tensor, weights: Optional[torch.Tensor]):
+        """One row per slot goes home to its (token,k) entry; the token's rank forms the (optionally
+        weighted) sum over its valid entries.  y [slots,H] -> out [T,H]."""
+        w = self.world
+        T, K, N, E = h.T, h.K, h.N, h.E
+        H = y.shape[1]
+        offs, total, maxima = _arena_geometry(h.maxima, H, K)
+        if self.is_cuda:
+            yield ("grow", total)
+        tabs = self._tables(offs, maxima, H, K, y.dtype)
+        if self.is_cuda:
+            if h.slots > 0:
+                self.ext.slot_rows_push(y.contiguous(), h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"),
+                                        offs["landing"])
+        else:
+            valid = (h.slot_tk >= 0).nonzero(as_tuple=True)[0]
+            rr = h.slot_row.long()[valid]
+            src = torch.bucketize(rr, h.recv_row_base.long()[1:], right=True)
+            writes = {}
+            for s in range(N):
+                m = src == s
+                writes[s] = [("landing", h.slot_tk.long()[valid[m]], y[valid[m]])]
+            yield ("push", writes)
+        yield ("barrier",)
+        out = torch.empty(T, H, dtype=y.dtype, device=y.device)
+        if T == 0:
+            return out
+        if self.is_cuda:
+            self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, E, out, weights)
+        else:
+            vmask = ((h.topk_idx >= 0) & (h.topk_idx < E)).float()
+            ww = vmask if weights is None else vmask * weights.float()
+            land = tabs["landing"][: T * K].float().view(T, K, H)
+            land = torch.where(vmask.bool()[:, :, None], land, torch.zeros((), dtype=torch.float32))
+            out.copy_((land * ww[:, :, None]).sum(1).to(y.dtype))
+        return out
+
     # ------------------------------------------------------------------ layer forward / backward
     def forward_gen(self, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, keep_for_backward=True, impl=None, num_sms=0):
         w = self.world
@@ -347,7 +384,7 @@ class EPEngine:
             yield ("barrier",)
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             if T > 0:
-                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out)
+                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out, None)
         else:
             y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del act
@@ -399,7 +436,7 @@ class EPEngine:
             T, K = h.T, h.K
             dx = torch.empty(T, h.H, dtype=grad_out.dtype, device=grad_out.device)
             if T > 0:
-                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, dx)
+                self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, dx, None)
             valid = (h.topk_idx >= 0) & (h.topk_idx < h.E)
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
             return dx, gtw, dW_gateup, dW_down
