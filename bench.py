@@ -47,7 +47,7 @@ def parse():
     p.add_argument("--config", default="dsv3", choices=sorted(CONFIGS))
     p.add_argument("--tokens", type=int, default=0, help="override tokens per rank")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--mode", default="auto", choices=["auto", "unfused", "fused"])
+    p.add_argument("--trace", action="store_true", help="print per-phase device times (rank 0, stderr) after the timed region")
     return p.parse_args()
 
 
@@ -231,6 +231,18 @@ def main():
         e2e = {"ms": e2e_ms, "wall_ms": e2e_wall, "h2d": h2d, "d2h": 4}
 
     clocks = sampler.stop() if sampler is not None else None
+    if args.trace and args.impl == "teramoe":
+        buf.trace(True)
+        for _ in range(3):
+            step_device()
+        rep = buf.trace_report()
+        buf.trace(False)
+        if rank == 0:
+            tot = sum(rep.values())
+            print("phase trace (ms, mean of 3 steps; events serialise nothing):", file=sys.stderr)
+            for k, v in rep.items():
+                print(f"  {k:40s} {v:8.3f}", file=sys.stderr)
+            print(f"  {'sum':40s} {tot:8.3f}", file=sys.stderr)
 
     def reduce_max(v):
         if world == 1:

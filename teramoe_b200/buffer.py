@@ -117,6 +117,14 @@ class Buffer(LowLatencyMixin):
             raise RuntimeError("Buffer was destroyed")
         return self._world.drive(gen)
 
+    def trace(self, on: bool = True) -> None:
+        """Start / stop recording per-phase device times of the fused layer calls (CUDA events)."""
+        self._engine.enable_trace(on)
+
+    def trace_report(self) -> dict:
+        """Mean milliseconds per phase since tracing started (and restart the record)."""
+        return self._engine.trace_report()
+
     def state(self) -> dict:
         """Sizes and configuration needed to rebuild an equivalent Buffer (nothing else persists between calls)."""
         return {"rank": self.rank, "group_size": self.group_size, "device": str(self.device), "num_nvl_bytes": self.num_nvl_bytes,

@@ -111,10 +111,11 @@ void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor ch
                                      i32(ndst, "ndst"), cur_stream()));
 }
 
-void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site) {
+void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site,
+                int64_t limit_ms) {
     c10::cuda::CUDAGuard guard(signal_ptrs.device());
     TM_CHECK_CUDA(tmoe::ep_barrier(u64(signal_ptrs, "signal_ptrs"), (int)rank, (int)N, (int)epoch, opt_status(status), (int)site,
-                                   cur_stream()));
+                                   (int)limit_ms, cur_stream()));
 }
 
 void dispatch_push(torch::Tensor x, torch::Tensor topk_idx, torch::Tensor topk_w, int64_t E, int64_t N, torch::Tensor send_slot,

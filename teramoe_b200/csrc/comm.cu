@@ -26,13 +26,15 @@ namespace tmoe {
 
 namespace {
 
-__global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site) {
+__global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, uint64_t limit_ns) {
     __threadfence_system();
     if ((int)threadIdx.x < N) {
         int* peer_sig = reinterpret_cast<int*>(signal_ptrs[threadIdx.x]);
         st_release_sys(peer_sig + rank, epoch);
         const int* my_sig = reinterpret_cast<const int*>(signal_ptrs[rank]);
-        wait_flag_ge_sys(my_sig + threadIdx.x, epoch, status, site + threadIdx.x);
+        // A peer that never arrives makes this wait run out: the status block then names the site
+        // (site + peer rank) and the kernel returns normally, so the context stays usable.
+        wait_flag_ge_sys(my_sig + threadIdx.x, epoch, status, site + threadIdx.x, limit_ns);
     }
 }
 
@@ -293,8 +295,10 @@ int grid_for_warps(long warps, int block) {
 
 }  // namespace
 
-cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, cudaStream_t stream) {
-    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site);
+cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms,
+                       cudaStream_t stream) {
+    const uint64_t limit_ns = limit_ms > 0 ? (uint64_t)limit_ms * 1000000ull : TMOE_WAIT_LIMIT_NS;
+    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns);
     return cudaGetLastError();
 }
 

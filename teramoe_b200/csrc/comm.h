@@ -18,7 +18,9 @@ struct SymOffsets {
     uint64_t gtw;        // [tok_cap*K] float   route-weight gradients arriving from expert ranks
 };
 
-cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, cudaStream_t stream);
+// limit_ms <= 0 selects the default wait limit (2 s).
+cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms,
+                       cudaStream_t stream);
 
 cudaError_t dispatch_push(const void* x, const void* topk_idx, int is64, const float* topk_w, int T, int K, int H, int E, int N,
                           const int* send_slot, const int* send_row, const int* land_off, const uint64_t* arena_ptrs,

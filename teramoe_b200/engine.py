@@ -110,6 +110,35 @@ class EPEngine:
         self.world = world
         self.is_cuda = world.is_cuda
         self.ext = world.ext if self.is_cuda else None
+        self._trace = None          # list of (phase name, CUDA event) while tracing
+
+    # ------------------------------------------------------------------ phase tracing
+    def enable_trace(self, on: bool = True) -> None:
+        """Record a CUDA event at every phase boundary of forward_gen / backward_gen (device time per
+        phase, read with trace_report).  The reference has no in-kernel or per-phase timers
+        (only a kineto helper in tests/utils.py:173-238)."""
+        self._trace = [] if (on and self.is_cuda) else None
+
+    def _mark(self, name: str) -> None:
+        if self._trace is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._trace.append((name, ev))
+
+    def trace_report(self) -> dict:
+        """Mean milliseconds per phase over the traced calls: time from the previous mark to this one."""
+        if not self._trace:
+            return {}
+        torch.cuda.synchronize()
+        acc, cnt = {}, {}
+        prev = None
+        for name, ev in self._trace:
+            if prev is not None and not name.endswith(":start"):
+                acc[name] = acc.get(name, 0.0) + prev.elapsed_time(ev)
+                cnt[name] = cnt.get(name, 0) + 1
+            prev = ev
+        self._trace = []
+        return {k: acc[k] / cnt[k] for k in acc}
 
     # ------------------------------------------------------------------ table access
     def _tables(self, offs, maxima, H, K, dtype):
@@ -365,19 +394,25 @@ class EPEngine:
         I = W_gateup.shape[1] // 2
         if W_gateup.shape[2] != H or tuple(W_down.shape[1:]) != (H, I):
             raise ValueError("weight shapes must be W_gateup [E_local, 2I, H] and W_down [E_local, H, I]")
+        self._mark("fwd:start")
         h = yield from self.layout_gen(topk_idx, num_experts)
+        self._mark("fwd:routing+layout")
         h.topk_weights = topk_weights
         tabs, offs = yield from self.dispatch_gen(h, x, topk_weights, with_meta=True)
+        self._mark("fwd:dispatch+barrier")
         self.snapshot_tables(h, tabs)
         saved_x = tabs["recv_x"][:h.rows].clone()
+        self._mark("fwd:save tables and X")
         st = w.status if self.is_cuda else None
         units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
         if USE_TMA_GATHER:
             act, preact = gemm.fwd_gateup(saved_x, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, gather_rows=h.slot_row)
         else:
             xperm = self.expand(saved_x, h)
+            self._mark("fwd:expand")
             act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del xperm
+        self._mark("fwd:gate_up GEMM+SwiGLU")
         if self.is_cuda and FUSED_COMBINE:
             gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, push=self._push_target(h, offs))
             del act
@@ -388,8 +423,10 @@ class EPEngine:
         else:
             y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del act
+            self._mark("fwd:down GEMM")
             out, _ = yield from self.combine_gen(h, y, tabs, offs)
             del y
+        self._mark("fwd:combine push+barrier+reduce")
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
 
@@ -402,7 +439,9 @@ class EPEngine:
         h = saved.handle
         El = W_gateup.shape[0]
         st = w.status if self.is_cuda else None
+        self._mark("bwd:start")
         tabs, offs = yield from self.dispatch_gen(h, grad_out, None, with_meta=False)
+        self._mark("bwd:dispatch+barrier")
         if USE_TMA_GATHER:
             dy_rows = tabs["recv_x"]      # token-once rows of grad_out, read through h.slot_row by the GEMMs
             dgu, act_w, parts = gemm.bwd_gradact(dy_rows, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
@@ -414,8 +453,10 @@ class EPEngine:
             units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
             pairs = units is not None
             dyperm = self.expand(tabs["recv_x"], h)
+            self._mark("bwd:expand dY")
             dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
                                                  units=units)
+            self._mark("bwd:grad_act GEMM+dSwiGLU")
             fused = self.is_cuda and FUSED_COMBINE
             if fused:
                 dxperm = None
@@ -424,10 +465,14 @@ class EPEngine:
                     self.ext.droute_push(parts, h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"), offs["gtw"])
             else:
                 dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
+            self._mark("bwd:dX GEMM")
             dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del dyperm
+            self._mark("bwd:dW_down GEMM")
             xperm = self.expand(saved.saved_x, h)
+            self._mark("bwd:expand X")
             dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
+            self._mark("bwd:dW_gateup GEMM")
             del xperm
         del dgu, act_w
         if dxperm is None and self.is_cuda and FUSED_COMBINE and not USE_TMA_GATHER:
@@ -441,6 +486,7 @@ class EPEngine:
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
             return dx, gtw, dW_gateup, dW_down
         dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
+        self._mark("bwd:combine push+barrier+reduce")
         return dx, gtw, dW_gateup, dW_down
 
 

@@ -132,12 +132,13 @@ class EPWorld:
             raise RuntimeError(f"teramoe_b200: a device-side wait ran out on rank {self.rank}: {names.get(s[0], s[0])} "
                                f"(site {s[1]}, block {s[2]}, detail {s[3]})")
 
-    def device_barrier(self, site: int = 500) -> None:
+    def device_barrier(self, site: int = 500, limit_ms: int = 0) -> None:
+        """Bounded all-rank barrier kernel on the current stream (limit_ms <= 0: the default 2 s)."""
         if self.size == 1:
             return
         ep = self.next_epoch()
         self.ext.ep_barrier(self.ptr_table(self.control, self.signal_offset, "control_sig"), self.rank, self.size, ep,
-                            self.status, site)
+                            self.status, site, limit_ms)
 
     def drive(self, gen: Generator):
         """Run a pipeline generator to completion in real (one process per rank) mode."""

@@ -27,7 +27,8 @@ def main():
         dtype, tol = torch.bfloat16, 2e-2
     else:
         dev = torch.device("cpu")
-        dist.init_process_group("gloo")
+        import datetime
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=15))
         dtype, tol = torch.float32, 1e-4
     group = dist.group.WORLD
 
@@ -78,6 +79,23 @@ def main():
             dist.destroy_process_group()
             return
         raise SystemExit("expected ValueError")
+    elif case == "absent":
+        # the last rank leaves before the first collective: the others must get an exception, not hang
+        if rank == world - 1:
+            print(f"WORKER_OK {rank}", flush=True)
+            os._exit(0)
+        buf = tm.Buffer(group, device=dev)
+        x = torch.randn(8, 64, dtype=dtype, device=dev)
+        idx = torch.zeros(8, 2, dtype=torch.int64, device=dev)
+        idx[:, 1] = 1
+        w = torch.ones(8, 2, device=dev)
+        Wg, Wd = torch.randn(1, 64, 64, dtype=dtype, device=dev), torch.randn(1, 64, 32, dtype=dtype, device=dev)
+        try:
+            buf.teramoe_autograd(x, idx, w, Wg, Wd, world)
+        except Exception as e:  # gloo reports the lost peer (connection closed / timeout)
+            print(f"WORKER_OK {rank} ({type(e).__name__})", flush=True)
+            os._exit(0)
+        raise SystemExit("expected an exception because a rank is absent")
     else:
         raise SystemExit(f"unknown case {case}")
     dist.barrier()

@@ -39,6 +39,11 @@ def test_gloo_mismatched_arguments_raise():
     _launch("gloo", "mismatch", 2)
 
 
+def test_gloo_absent_rank_is_detected():
+    """Host-side failure detection: a rank that leaves makes the others raise instead of hanging."""
+    _launch("gloo", "absent", 2, timeout=120)
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 def test_nccl_layer_all_gpus():
