@@ -113,7 +113,9 @@ def main():
     if args.impl == "nccl":
         from teramoe_b200.parallel.nccl_baseline import NcclMoEBaseline
         layer = NcclMoEBaseline(group, E)
-        run_layer = lambda x, idx, w: layer(x, idx, w, Wg, Wd)
+        # the baseline keeps its gate/up weights in the layout a library SwiGLU prefers (gate rows, then up rows)
+        Wg = NcclMoEBaseline.to_chunked(Wg.detach()).requires_grad_(True)
+        run_layer = lambda x, idx, w: layer(x, idx, w, Wg, Wd, chunked=True)
     else:
         buf = tm.Buffer(group, int(2e9), int(1e9) if world > 8 else 0, explicitly_destroy=True)
         run_layer = lambda x, idx, w: buf.teramoe_autograd(x, idx, w, Wg, Wd, E, num_dispatch_sms=48, num_combine_sms=48)

@@ -42,7 +42,13 @@ class NcclMoEBaseline:
         self.E = num_experts
         self.El = num_experts // self.N
 
-    def __call__(self, x, topk_idx, topk_weights, W_gateup, W_down):
+    @staticmethod
+    def to_chunked(W_gateup: torch.Tensor) -> torch.Tensor:
+        """Element-interleaved [E,2I,H] -> gate rows then up rows (the layout a library SwiGLU wants)."""
+        return torch.cat([W_gateup[:, 0::2], W_gateup[:, 1::2]], dim=1).contiguous()
+
+    def __call__(self, x, topk_idx, topk_weights, W_gateup, W_down, chunked: bool = False):
+        """`chunked=True`: W_gateup holds all gate rows, then all up rows (no strided slicing)."""
         N, E, El = self.N, self.E, self.El
         T, H = x.shape
         K = topk_idx.shape[1]
@@ -86,7 +92,11 @@ class NcclMoEBaseline:
                 continue
             a = xe[o:o + c]
             gu = a @ W_gateup[le].t()
-            act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+            if chunked:
+                g, u = gu.chunk(2, dim=1)
+                act = torch.nn.functional.silu(g) * u
+            else:
+                act = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
             outs.append(act @ W_down[le].t())
             o += c
         ye = torch.cat(outs) if outs else xe.new_zeros(0, H)
