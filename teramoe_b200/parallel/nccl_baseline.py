@@ -35,6 +35,21 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
+class _PermuteRows(torch.autograd.Function):
+    """y = x[perm] for a permutation `perm`; the gradient is a gather through the inverse permutation
+    (no atomics), which is what a fused permute kernel of a training framework does."""
+
+    @staticmethod
+    def forward(ctx, x, perm, inv):
+        ctx.save_for_backward(inv)
+        return x[perm]
+
+    @staticmethod
+    def backward(ctx, g):
+        (inv,) = ctx.saved_tensors
+        return g[inv], None, None
+
+
 class NcclMoEBaseline:
     def __init__(self, group: Optional[dist.ProcessGroup], num_experts: int):
         self.group = group
@@ -69,7 +84,14 @@ class NcclMoEBaseline:
         cnt_h, recv_h = cnt.cpu(), recv_cnt.cpu()                  # host sync, as in Megatron's all-to-all dispatcher
         in_splits = cnt_h.sum(1).tolist()
         out_splits = recv_h.sum(1).tolist()
-        xs = x[tok]                                                # [entries, H] permuted by expert (kept by autograd)
+        all_valid = ent.numel() == T * K
+        if all_valid:
+            # permutation path: every (token,k) entry is routed, so permute / un-permute are pure gathers
+            inv_ent = torch.empty_like(ent)
+            inv_ent[ent] = torch.arange(ent.numel(), device=x.device)
+            xs = _PermuteRows.apply(x.unsqueeze(1).expand(T, K, H).reshape(T * K, H), ent, inv_ent)
+        else:
+            xs = x[tok]                                            # [entries, H] permuted by expert (kept by autograd)
         recv = _AllToAll.apply(xs, out_splits, in_splits, self.group)
         # rows arrive grouped by (source, local expert); regroup by local expert
         S = recv.shape[0]
@@ -82,7 +104,9 @@ class NcclMoEBaseline:
                 if seg[j] > 0:
                     pieces.append(torch.arange(int(starts[j]), int(starts[j] + seg[j])))
         sort_idx = (torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.long)).to(x.device)
-        xe = recv[sort_idx]
+        inv = torch.empty_like(sort_idx)
+        inv[sort_idx] = torch.arange(S, device=x.device)
+        xe = _PermuteRows.apply(recv, sort_idx, inv)
         per_expert = recv_h.sum(0).tolist()
         outs = []
         o = 0
@@ -100,10 +124,11 @@ class NcclMoEBaseline:
             outs.append(act @ W_down[le].t())
             o += c
         ye = torch.cat(outs) if outs else xe.new_zeros(0, H)
-        inv = torch.empty_like(sort_idx)
-        inv[sort_idx] = torch.arange(S, device=x.device)
-        y = ye[inv]
+        y = _PermuteRows.apply(ye, inv, sort_idx)
         back = _AllToAll.apply(y, in_splits, out_splits, self.group)
+        if all_valid:
+            yk = _PermuteRows.apply(back, inv_ent, ent).view(T, K, H)
+            return (yk * topk_weights.to(back.dtype).unsqueeze(-1)).sum(1)
         wsel = topk_weights.reshape(-1)[ent].to(back.dtype)
         out = torch.zeros(T, H, dtype=torch.float32, device=x.device).index_add(0, tok, (back * wsel[:, None]).float())
         return out.to(x.dtype)

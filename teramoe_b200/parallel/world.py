@@ -117,6 +117,12 @@ class EPWorld:
         self.data_bytes = new_bytes
         self._ptr_cache = {k: v for k, v in self._ptr_cache.items() if k.startswith("control")}
 
+    def side_stream(self):
+        """High-priority stream for communication kernels that overlap compute."""
+        if getattr(self, "_side_stream", None) is None:
+            self._side_stream = torch.cuda.Stream(self.device, priority=-1)
+        return self._side_stream
+
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch

@@ -98,3 +98,32 @@ def test_dispatch_combine_unfused_api():
     # cached handle: payload only
     recv2, *_ = buf.deepep_dispatch(x * 2, handle=handle)
     assert torch.equal(recv2, x * 2)
+
+
+def test_reference_accuracy_case_ep1():
+    """The reference's accuracy case (tests/test_teramoe_accuracy.py:53-57, :185-243, :390-395): T=4096, H=2048, I=2048,
+    16 experts, top-8, x ~ 0.1 N(0,1), W ~ 0.02 N(0,1); output, dX, dW_gateup, dW_down, dTopKWeights must each satisfy
+    max_abs <= 1e-2, calc_diff <= 1e-5, cosine >= 0.99 against an fp32 evaluation of the same layer."""
+    torch.manual_seed(42)
+    T, H, I, E, K = 4096, 2048, 2048, 16, 8
+    dev = "cuda"
+    x = (torch.randn(T, H, device=dev) * 0.1).to(torch.bfloat16)
+    Wg = (torch.randn(E, 2 * I, H, device=dev) * 0.02).to(torch.bfloat16)
+    Wd = (torch.randn(E, H, I, device=dev) * 0.02).to(torch.bfloat16)
+    scores = torch.sigmoid(torch.randn(T, E, device=dev))
+    top = torch.topk(scores, K, dim=1)
+    idx, w = top.indices, (top.values / top.values.sum(1, keepdim=True)).float()
+    go = (torch.randn(T, H, device=dev) * 0.1).to(torch.bfloat16)
+    buf = tm.Buffer(None, int(2e9), int(1e9), explicitly_destroy=True)      # the documented constructor call
+    xl, wl = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    Wgl, Wdl = Wg.clone().requires_grad_(True), Wd.clone().requires_grad_(True)
+    out = buf.teramoe_autograd(xl, idx, wl, Wgl, Wdl, E, num_dispatch_sms=48, num_combine_sms=48, compute_batch_size=4096)
+    out.backward(go)
+    xr, wr = x.float().requires_grad_(True), w.clone().requires_grad_(True)
+    Wgr, Wdr = Wg.float().requires_grad_(True), Wd.float().requires_grad_(True)
+    ref = tm.moe_reference(xr, idx, wr, Wgr, Wdr)
+    ref.backward(go.float())
+    for name, got, want in (("output", out, ref), ("dX", xl.grad, xr.grad), ("dTopKWeights", wl.grad, wr.grad),
+                            ("dW_gateup", Wgl.grad, Wgr.grad), ("dW_down", Wdl.grad, Wdr.grad)):
+        assert_close_bf16(got.float(), want.detach().float(), name)
+    buf.destroy()
