@@ -343,6 +343,16 @@ class Buffer(LowLatencyMixin):
             raise ValueError("no SMs left for compute")
         if num_experts % self.group_size:
             raise ValueError("num_experts must be divisible by the number of ranks")
+        if W_gateup.dim() != 3 or W_down.dim() != 3 or W_gateup.shape[1] % 2:
+            raise ValueError("expected W_gateup [E_local, 2I, H] and W_down [E_local, H, I]")
+        if x.is_cuda:
+            H, I = x.shape[1], W_gateup.shape[1] // 2
+            if H % 64 or I % 64:
+                raise ValueError("the tcgen05 kernels need hidden and intermediate sizes that are multiples of 64")
+            if not (W_gateup.is_contiguous() and W_down.is_contiguous()):
+                raise ValueError("W_gateup and W_down must be contiguous")
+            if W_gateup.dtype != torch.bfloat16 or W_down.dtype != torch.bfloat16:
+                raise ValueError("weights must be bf16 on CUDA")
 
     def teramoe_autograd(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, W_gateup: torch.Tensor,
                          W_down: torch.Tensor, num_experts: int, num_dispatch_sms: int = 24, num_combine_sms: int = 24,

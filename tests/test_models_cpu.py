@@ -33,3 +33,32 @@ def test_block_trains_on_cpu():
         losses.append(loss.item())
     assert losses[-1] < losses[0]
     assert block.moe.router.weight.grad is not None and block.moe.W_gateup.grad.abs().sum() > 0
+
+
+def test_two_layers_share_one_buffer():
+    """Forward of layer 2 runs before backward of layer 1: saved state must not live in reused buffers."""
+    torch.manual_seed(2)
+    buf = tm.Buffer(None, device="cpu")
+    T, H, I, E, K = 48, 64, 96, 8, 2
+    x = torch.randn(T, H)
+    params = []
+    for _ in range(2):
+        params.append((torch.randn(E, 2 * I, H) * 0.1, torch.randn(E, H, I) * 0.1, torch.randn(T, E)))
+
+    def run(layer_fn):
+        leaves = [x.clone().requires_grad_(True)]
+        h = leaves[0]
+        ws = []
+        for Wg, Wd, logits in params:
+            Wg, Wd = Wg.clone().requires_grad_(True), Wd.clone().requires_grad_(True)
+            top = torch.topk(logits, K, dim=1)
+            w = torch.softmax(top.values, 1).requires_grad_(True)
+            h = h + layer_fn(h, top.indices, w, Wg, Wd)
+            ws += [Wg, Wd, w]
+        h.pow(2).sum().backward()
+        return [leaves[0].grad] + [p.grad for p in ws]
+
+    got = run(lambda h, idx, w, Wg, Wd: buf.teramoe_autograd(h, idx, w, Wg, Wd, E))
+    want = run(lambda h, idx, w, Wg, Wd: tm.moe_reference(h, idx, w, Wg, Wd))
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=1e-4, rtol=1e-4)
