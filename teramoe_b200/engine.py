@@ -139,8 +139,13 @@ class EPEngine:
         torch.cuda.synchronize()
         acc, cnt = {}, {}
         prev = None
+        cur_phase = "fwd"
         for name, ev in self._trace:
+            if name.endswith(":start"):
+                cur_phase = name.split(":")[0]
             if prev is not None and not name.endswith(":start"):
+                name = name if not name.startswith("  ") else cur_phase + name
+
                 acc[name] = acc.get(name, 0.0) + prev.elapsed_time(ev)
                 cnt[name] = cnt.get(name, 0) + 1
             prev = ev
@@ -258,7 +263,9 @@ class EPEngine:
                 tabs["slot_tk"].fill_(-1)
                 tabs["row_slots"].fill_(-1)
             yield ("push", _cpu_dispatch_writes(h, x, topk_weights, with_meta))
+        self._mark("  dispatch push kernel")
         yield ("barrier",)
+        self._mark("  dispatch barrier")
         return tabs, offs
 
     def snapshot_tables(self, h: LayerHandle, tabs) -> None:
@@ -319,8 +326,12 @@ class EPEngine:
         writes = self._combine_push(h, y, offs, droute_parts)
         if writes is not None:
             yield ("push", writes)
+        self._mark("  combine push kernel")
         yield ("barrier",)
-        return self._combine_reduce(h, tabs, y.dtype, y.device, droute_parts is not None)
+        self._mark("  combine barrier")
+        res = self._combine_reduce(h, tabs, y.dtype, y.device, droute_parts is not None)
+        self._mark("  combine reduce kernel")
+        return res
 
     def combine_rows_gen(self, h: LayerHandle, x: torch.Tensor, recv_topk_weights: Optional[torch.Tensor]):
         """Un-fused combine of one row per received token (x [rows,H]); optionally carries the
@@ -406,7 +417,7 @@ class EPEngine:
         self._mark("fwd:routing+layout")
         h.topk_weights = topk_weights
         tabs, offs = yield from self.dispatch_gen(h, x, topk_weights, with_meta=True)
-        self._mark("fwd:dispatch+barrier")
+        self._mark("fwd:dispatch (rest)")
         self.snapshot_tables(h, tabs)
         saved_x = tabs["recv_x"][:h.rows].clone()
         self._mark("fwd:save tables and X")
@@ -433,7 +444,7 @@ class EPEngine:
             self._mark("fwd:down GEMM")
             out, _ = yield from self.combine_gen(h, y, tabs, offs)
             del y
-        self._mark("fwd:combine push+barrier+reduce")
+        self._mark("fwd:combine (rest)")
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
 
@@ -448,7 +459,7 @@ class EPEngine:
         st = w.status if self.is_cuda else None
         self._mark("bwd:start")
         tabs, offs = yield from self.dispatch_gen(h, grad_out, None, with_meta=False)
-        self._mark("bwd:dispatch+barrier")
+        self._mark("bwd:dispatch (rest)")
         if USE_TMA_GATHER:
             dy_rows = tabs["recv_x"]      # token-once rows of grad_out, read through h.slot_row by the GEMMs
             dgu, act_w, parts = gemm.bwd_gradact(dy_rows, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
@@ -513,7 +524,7 @@ class EPEngine:
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
             return dx, gtw, dW_gateup, dW_down
         dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
-        self._mark("bwd:combine push+barrier+reduce")
+        self._mark("bwd:combine (rest)")
         return dx, gtw, dW_gateup, dW_down
 
 
