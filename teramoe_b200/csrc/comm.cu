@@ -38,6 +38,20 @@ __global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, 
     }
 }
 
+// Warp-wide row copy (nvec 16-byte vectors) with four loads in flight per lane before the stores, so that
+// a warp keeps 2 KB outstanding instead of 512 bytes.
+__device__ __forceinline__ void warp_copy_row(int4* dst, const int4* src, int nvec, int lane) {
+    int i = lane;
+    for (; i + 96 < nvec; i += 128) {
+        const int4 a = src[i], b = src[i + 32], c = src[i + 64], d = src[i + 96];
+        st_na_v4(dst + i, a);
+        st_na_v4(dst + i + 32, b);
+        st_na_v4(dst + i + 64, c);
+        st_na_v4(dst + i + 96, d);
+    }
+    for (; i < nvec; i += 32) st_na_v4(dst + i, src[i]);
+}
+
 __device__ __forceinline__ int64_t load_topk(const void* idx, int is64, long i) {
     return is64 ? reinterpret_cast<const int64_t*>(idx)[i] : (int64_t) reinterpret_cast<const int32_t*>(idx)[i];
 }
@@ -58,7 +72,7 @@ dispatch_push_kernel(const __nv_bfloat16* x, const void* topk_idx, int is64, con
             const int d = __ffs(m) - 1;
             const int row = __shfl_sync(0xffffffffu, my_row, d);
             int4* dst = reinterpret_cast<int4*>(arena_ptrs[d] + so.recv_x + (uint64_t)row * H * 2);
-            for (int i = lane; i < nvec; i += 32) st_na_v4(dst + i, src[i]);
+            warp_copy_row(dst, src, nvec, lane);
         }
         if (with_meta) {
             // per-slot tables: lane k owns entry (t,k)
@@ -111,7 +125,7 @@ expand_rows_kernel(const __nv_bfloat16* rows, const int* slot_row, __nv_bfloat16
         int4* dst = reinterpret_cast<int4*>(out + (long)s * H);
         if (r >= 0) {
             const int4* src = reinterpret_cast<const int4*>(rows + (long)r * H);
-            for (int i = lane; i < nvec; i += 32) dst[i] = src[i];
+            warp_copy_row(dst, src, nvec, lane);
         } else {
             for (int i = lane; i < nvec; i += 32) dst[i] = make_int4(0, 0, 0, 0);
         }
@@ -150,9 +164,23 @@ combine_push_kernel(const __nv_bfloat16* y, const int* row_slots, const int* row
         } else if (nsl == 1) {
             const int s0 = __shfl_sync(0xffffffffu, my_slot, 0);
             const int4* p = reinterpret_cast<const int4*>(y + (long)s0 * H);
-            for (int i = lane; i < nvec; i += 32) st_na_v4(dst + i, p[i]);
+            warp_copy_row(dst, p, nvec, lane);
         } else {
-            for (int i = lane; i < nvec; i += 32) {
+            int i = lane;
+            for (; i + 32 < nvec; i += 64) {        // two vectors per lane in flight for every source row
+                float acc0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                float acc1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int j = 0; j < nsl; ++j) {
+                    const int sj = __shfl_sync(0xffffffffu, my_slot, j);
+                    const int4* row = reinterpret_cast<const int4*>(y + (long)sj * H);
+                    const int4 v0 = row[i], v1 = row[i + 32];
+                    accum_bf16x8(acc0, v0);
+                    accum_bf16x8(acc1, v1);
+                }
+                st_na_v4(dst + i, pack_bf16x8(acc0));
+                st_na_v4(dst + i + 32, pack_bf16x8(acc1));
+            }
+            for (; i < nvec; i += 32) {
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int j = 0; j < nsl; ++j) {
                     const int sj = __shfl_sync(0xffffffffu, my_slot, j);
@@ -206,7 +234,7 @@ slot_rows_push_kernel(const __nv_bfloat16* y, const int* slot_tk, const int* slo
         while (src + 1 < N && rr >= recv_row_base[src + 1]) ++src;
         int4* dst = reinterpret_cast<int4*>(arena_ptrs[src] + landing_off + (uint64_t)tk * H * 2);
         const int4* p = reinterpret_cast<const int4*>(y + (long)s * H);
-        for (int i = lane; i < nvec; i += 32) st_na_v4(dst + i, p[i]);
+        warp_copy_row(dst, p, nvec, lane);
     }
 }
 
@@ -223,20 +251,41 @@ combine_reduce_slots_kernel(const __nv_bfloat16* landing, const void* topk_idx, 
         if (lane < K) e = load_topk(topk_idx, is64, (long)t * K + lane);
         const uint32_t valid = __ballot_sync(0xffffffffu, e >= 0 && e < E);
         int4* dst = reinterpret_cast<int4*>(out + (long)t * H);
+        if (weights == nullptr) {
+            int i = lane;
+            for (; i + 32 < nvec; i += 64) {    // two vectors per lane and entry in flight
+                float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (uint32_t m = valid; m != 0; m &= m - 1) {
+                    const int k = __ffs(m) - 1;
+                    const int4* row = reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H);
+                    const int4 v0 = ld_nc_v4(row + i), v1 = ld_nc_v4(row + i + 32);
+                    accum_bf16x8(a0, v0);
+                    accum_bf16x8(a1, v1);
+                }
+                dst[i] = pack_bf16x8(a0);
+                dst[i + 32] = pack_bf16x8(a1);
+            }
+            for (; i < nvec; i += 32) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (uint32_t m = valid; m != 0; m &= m - 1) {
+                    const int k = __ffs(m) - 1;
+                    accum_bf16x8(acc, ld_nc_v4(reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H) + i));
+                }
+                dst[i] = pack_bf16x8(acc);
+            }
+            continue;
+        }
         for (int i = lane; i < nvec; i += 32) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (uint32_t m = valid; m != 0; m &= m - 1) {
                 const int k = __ffs(m) - 1;
                 const int4 v = ld_nc_v4(reinterpret_cast<const int4*>(landing + ((long)t * K + k) * H) + i);
-                if (weights == nullptr) {
-                    accum_bf16x8(acc, v);
-                } else {
-                    float one[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    accum_bf16x8(one, v);
-                    const float wk = weights[(long)t * K + k];
+                float one[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                accum_bf16x8(one, v);
+                const float wk = weights[(long)t * K + k];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] += wk * one[j];
-                }
+                for (int j = 0; j < 8; ++j) acc[j] += wk * one[j];
             }
             dst[i] = pack_bf16x8(acc);
         }

@@ -334,6 +334,7 @@ cudaError_t gemm_fwd_down(const void* act, const void* w_down, void* y, const MG
     g.status = status;
     if (push != nullptr) {
         set_push(g, *push);
+        if (lay.unit_blk != nullptr) return gemm2_mgroup(4, act, w_down, g, max_mblocks * BM, I, num_local_experts * H, I, num_sms, stream);
         return launch<false, false, false, kEpiPush, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
     }
     if (lay.unit_blk != nullptr) return gemm2_mgroup(1, act, w_down, g, max_mblocks * BM, I, num_local_experts * H, I, num_sms, stream);
@@ -409,6 +410,8 @@ cudaError_t gemm_bwd_dx(const void* dgu, const void* w_gateup, void* dxperm, con
     g.status = status;
     if (push != nullptr) {
         set_push(g, *push);
+        if (lay.unit_blk != nullptr)
+            return gemm2_mgroup(5, dgu, w_gateup, g, max_mblocks * BM, 2 * I, num_local_experts * 2 * I, H, num_sms, stream);
         return launch<false, true, false, kEpiPush, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
     }
     if (lay.unit_blk != nullptr)

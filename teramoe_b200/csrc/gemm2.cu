@@ -29,10 +29,15 @@ using namespace detail;
 
 namespace {
 
-constexpr int kStages2 = 6;
+// Pipeline depth: six 32 KB stages; the push epilogue gives one stage up for its staging buffers.
+__host__ __device__ constexpr int stages_for(int epi) { return epi == kEpiPush ? 5 : 6; }
+constexpr int kPushRowBytes = 128 + 16;                        // 64 bf16 columns + pad (bank-conflict-free rows)
+constexpr int kPushWarpBytes = 32 * kPushRowBytes;             // one epilogue warp stages 32 rows x 64 columns
+__host__ __device__ constexpr int smem_bytes_for(int epi) {
+    return stages_for(epi) * (16384 + 16384) + 1024 + 256 + (epi == kEpiPush ? kEpiWarps * kPushWarpBytes : 0);
+}
 constexpr int kBHalfBytes = (BN / 2) * BK * 2;                 // 16 KB: this CTA's half of the B tile
 constexpr int kStageBytes2 = kAStageBytes + kBHalfBytes;       // 32 KB
-constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 256;
 
 constexpr int kSuperU = 8;                                      // units per L2 super-group
 
@@ -82,10 +87,12 @@ template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ GemmArgs g) {
+    constexpr int kStages2 = stages_for(EPI);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bar_base = smem_base + kStages2 * kStageBytes2;
+    const uint32_t push_stage_base = bar_base + 256;           // kEpiPush: staging rows of the epilogue warps
     auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // used in CTA 0 only
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages2 + s); };          // one per CTA
     auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * kStages2 + s); };      // one per CTA
@@ -225,7 +232,58 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 row_ok = m < g.m_total;
                 row = (long)tile.group * g.m_total + m;
             }
-            if (live) epilogue_thread<EPI>(g, taddr0, row_ok ? row : 0, row_ok, n0, tile.n_blk * 2 + h, tile.nk == 0);
+            if constexpr (EPI == kEpiPush) {
+                // Combine fused into the GEMM: this warp's 32 rows x 128 columns leave for the ranks that own the
+                // tokens.  Rows are staged in shared memory 64 columns at a time so that every store
+                // instruction writes four 128-byte row segments (coalesced peer stores over NVLink).
+                unsigned long long dst_row = 0ull;
+                if (live) {
+                    const int tk = g.slot_tk[row];
+                    if (tk >= 0) {
+                        const int rr = g.slot_row[row];
+                        int src = 0;
+                        while (src + 1 < g.num_ranks && rr >= g.recv_row_base[src + 1]) ++src;
+                        dst_row = g.push_ptrs[src] + g.push_off + (unsigned long long)tk * g.ldd * 2ull;
+                    }
+                }
+                const uint32_t my_stage = push_stage_base + (uint32_t)(warp - 4) * kPushWarpBytes;
+                const uint32_t my_row_smem = my_stage + (uint32_t)lane * kPushRowBytes;
+#pragma unroll 1
+                for (int cg = 0; cg < 2; ++cg) {
+#pragma unroll
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        uint32_t acc[32];
+                        tmem_ld_x32(taddr0 + (uint32_t)(cg * 64 + c2 * 32), acc);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint32_t p0 = pack_bf16x2(__uint_as_float(acc[8 * v]), __uint_as_float(acc[8 * v + 1]));
+                            const uint32_t p1 = pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
+                            const uint32_t p2 = pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
+                            const uint32_t p3 = pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row_smem + (uint32_t)(c2 * 64 + v * 16)),
+                                         "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
+                        }
+                    }
+                    __syncwarp();
+                    const int col0 = n0 + cg * 64;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rsel = it * 4 + (lane >> 3);
+                        const int seg = lane & 7;
+                        const unsigned long long p = __shfl_sync(0xffffffffu, dst_row, rsel);
+                        if (p != 0ull && col0 + seg * 8 + 8 <= g.n_total) {
+                            int4 v;
+                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                         : "r"(my_stage + (uint32_t)rsel * kPushRowBytes + (uint32_t)seg * 16));
+                            st_na_v4(reinterpret_cast<void*>(p + (unsigned long long)(col0 + seg * 8) * 2ull), v);
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else {
+                if (live) epilogue_thread<EPI>(g, taddr0, row_ok ? row : 0, row_ok, n0, tile.n_blk * 2 + h, tile.nk == 0);
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(as), 0));
@@ -243,6 +301,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
 cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms, cudaStream_t stream) {
     auto kern = grouped_gemm2_kernel<A_MN, B_MN, KGROUP, EPI>;
+    constexpr int kSmemBytes2 = smem_bytes_for(EPI);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
@@ -261,12 +320,12 @@ cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs
 
 cudaError_t gemm2_mgroup(int kind, const void* a, const void* b, const GemmArgs& g_in, int a_rows, int a_cols, int b_rows, int b_cols,
                          int num_sms, cudaStream_t stream) {
-    // kind: 0 gate_up+SwiGLU, 1 down, 2 grad_act+dSwiGLU, 3 dX
+    // kind: 0 gate_up+SwiGLU, 1 down, 2 grad_act+dSwiGLU, 3 dX, 4 down with pushed rows, 5 dX with pushed rows
     GemmArgs g = g_in;
     CUtensorMap ma, mb;
     cudaError_t e;
     if ((e = make_map(&ma, a, (uint64_t)a_rows, a_cols, BK, BM)) != cudaSuccess) return e;
-    const bool b_mn = (kind == 2 || kind == 3);
+    const bool b_mn = (kind == 2 || kind == 3 || kind == 5);
     if ((e = b_mn ? make_map(&mb, b, (uint64_t)b_rows, b_cols, 64, BK) : make_map(&mb, b, (uint64_t)b_rows, b_cols, BK, BN / 2)) != cudaSuccess)
         return e;
     const int tiles = g.max_units * g.num_n_blocks;
@@ -275,6 +334,8 @@ cudaError_t gemm2_mgroup(int kind, const void* a, const void* b, const GemmArgs&
         case 0: return launch2<false, false, false, kEpiSwiGLU>(ma, mb, g, tiles, sms, stream);
         case 1: return launch2<false, false, false, kEpiStore>(ma, mb, g, tiles, sms, stream);
         case 2: return launch2<false, true, false, kEpiDSwiGLU>(ma, mb, g, tiles, sms, stream);
+        case 4: return launch2<false, false, false, kEpiPush>(ma, mb, g, tiles, sms, stream);
+        case 5: return launch2<false, true, false, kEpiPush>(ma, mb, g, tiles, sms, stream);
         default: return launch2<false, true, false, kEpiStore>(ma, mb, g, tiles, sms, stream);
     }
 }

@@ -38,12 +38,13 @@ USE_TMA_GATHER = os.environ.get("TERAMOE_TMA_GATHER", "0") == "1"
 # kernels and 6-27 % faster (csrc/gemm2.cu).  "0" selects the one-CTA kernels.
 USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "1") == "1"
 # Combine fused into the GEMM: the epilogues of the down GEMM (forward) and the dX GEMM (backward) store
-# every output row straight into the landing table of the token's rank (peer stores over NVLink, tile by
-# tile, while the tensor cores work on the next tile).  "0" = separate combine_push kernel.
-# Measured at EP=4 (H=7168, I=2048, top-8): 23.8 ms per step against 19.5 ms with the separate kernel:
-# 64-byte row fragments stored from the epilogue are a poor NVLink payload and stall the epilogue
-# warps, and one row per (token,k) is 1.5x the bytes of one row per (token, rank).  Off by default.
-FUSED_COMBINE = os.environ.get("TERAMOE_FUSED_COMBINE", "0") == "1"
+# every output row straight into the landing table of the token's rank (coalesced peer stores over
+# NVLink staged through shared memory, tile by tile, while the tensor cores work on the next tile).
+# Measured at EP=4 (H=7168, I=2048, top-8): the down GEMM takes 1.40 ms with the pushed combine against
+# 1.39 ms without, i.e. the all-to-all is hidden; the step drops from 17.3 to 16.8 ms.  (A first version
+# that stored 64-byte fragments straight from the epilogue registers cost +4 ms.)  "0" = separate
+# combine_push kernel (one row per (token, rank) on the wire instead of one per (token, k)).
+FUSED_COMBINE = os.environ.get("TERAMOE_FUSED_COMBINE", "1") == "1"
 # Backward, more than one rank: the combine push of dX (+ barrier) can run on a side stream on a few SMs
 # while the two weight-gradient GEMMs, which nothing downstream waits for, run on the remaining SMs.
 # Measured at EP=2 (H=7168, I=2048): 18.0 ms per step with the overlap against 16.7 ms without (the
@@ -432,12 +433,15 @@ class EPEngine:
             del xperm
         self._mark("fwd:gate_up GEMM+SwiGLU")
         if self.is_cuda and FUSED_COMBINE:
-            gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, push=self._push_target(h, offs))
+            gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units, push=self._push_target(h, offs))
             del act
+            self._mark("fwd:down GEMM + pushed combine")
             yield ("barrier",)
+            self._mark("fwd:combine barrier")
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             if T > 0:
                 self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out, None)
+            self._mark("fwd:combine reduce (per-entry rows)")
         else:
             y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del act
@@ -478,9 +482,10 @@ class EPEngine:
             fused = self.is_cuda and FUSED_COMBINE
             if fused:
                 dxperm = None
-                gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, push=self._push_target(h, offs))
+                gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units, push=self._push_target(h, offs))
                 if h.slots > 0:
                     self.ext.droute_push(parts, h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"), offs["gtw"])
+                self._mark("bwd:dX GEMM + pushed combine")
             else:
                 dxperm = gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             self._mark("bwd:dX GEMM")
@@ -516,12 +521,14 @@ class EPEngine:
         if dxperm is None and self.is_cuda and FUSED_COMBINE and not USE_TMA_GATHER:
             # weight gradients were enqueued after the push so they overlap the other ranks' pushes
             yield ("barrier",)
+            self._mark("bwd:combine barrier")
             T, K = h.T, h.K
             dx = torch.empty(T, h.H, dtype=grad_out.dtype, device=grad_out.device)
             if T > 0:
                 self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, dx, None)
             valid = (h.topk_idx >= 0) & (h.topk_idx < h.E)
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
+            self._mark("bwd:combine reduce (per-entry rows)")
             return dx, gtw, dW_gateup, dW_down
         dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
         self._mark("bwd:combine (rest)")

@@ -73,7 +73,7 @@ def fwd_down(act, w_down, mblock_expert, num_mblocks, status=None, num_sms=0, un
     S, I = act.shape
     H = w_down.shape[1]
     if push is not None:
-        load_ext().gemm_fwd_down(act, w_down, None, _lay(mblock_expert, num_mblocks, None), status, num_sms, push[0], push[1])
+        load_ext().gemm_fwd_down(act, w_down, None, _lay(mblock_expert, num_mblocks, units), status, num_sms, push[0], push[1])
         return None
     y = torch.empty(S, H, dtype=act.dtype, device=act.device)
     if act.is_cuda:
@@ -105,7 +105,7 @@ def bwd_dx(dgu, w_gateup, mblock_expert, num_mblocks, status=None, num_sms=0, un
     S = dgu.shape[0]
     H = w_gateup.shape[2]
     if push is not None:
-        load_ext().gemm_bwd_dx(dgu, w_gateup, None, _lay(mblock_expert, num_mblocks, None), status, num_sms, push[0], push[1])
+        load_ext().gemm_bwd_dx(dgu, w_gateup, None, _lay(mblock_expert, num_mblocks, units), status, num_sms, push[0], push[1])
         return None
     dx = torch.empty(S, H, dtype=dgu.dtype, device=dgu.device)
     if dgu.is_cuda:
