@@ -44,7 +44,18 @@ USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "1") == "1"
 # 1.39 ms without, i.e. the all-to-all is hidden; the step drops from 17.3 to 16.8 ms.  (A first version
 # that stored 64-byte fragments straight from the epilogue registers cost +4 ms.)  "0" = separate
 # combine_push kernel (one row per (token, rank) on the wire instead of one per (token, k)).
-FUSED_COMBINE = os.environ.get("TERAMOE_FUSED_COMBINE", "1") == "1"
+# The push is only hidden when the GEMM lasts longer than its transfer: per pushed byte the down GEMM
+# does I FLOPs and the dX GEMM 2I.  Measured with I=512 at EP=4 the pushed down GEMM took 4.1 ms (plain
+# GEMM 1.07 ms + separate push 1.29 ms) and the step 21.8 ms against 15.2 ms, so "auto" (the default)
+# fuses forward when I >= 1536 and backward when I >= 768, and always on a single rank.
+_FUSED_MODE = os.environ.get("TERAMOE_FUSED_COMBINE", "auto")
+FUSED_COMBINE = _FUSED_MODE != "0"
+
+
+def use_fused_combine(I: int, num_ranks: int, backward: bool) -> bool:
+    if _FUSED_MODE in ("0", "1"):
+        return _FUSED_MODE == "1"
+    return num_ranks == 1 or I >= (768 if backward else 1536)
 # Backward, more than one rank: the combine push of dX (+ barrier) can run on a side stream on a few SMs
 # while the two weight-gradient GEMMs, which nothing downstream waits for, run on the remaining SMs.
 # Measured at EP=2 (H=7168, I=2048): 18.0 ms per step with the overlap against 16.7 ms without (the
@@ -432,7 +443,7 @@ class EPEngine:
             act, preact = gemm.fwd_gateup(xperm, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del xperm
         self._mark("fwd:gate_up GEMM+SwiGLU")
-        if self.is_cuda and FUSED_COMBINE:
+        if self.is_cuda and use_fused_combine(I, w.size, False):
             gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units, push=self._push_target(h, offs))
             del act
             self._mark("fwd:down GEMM + pushed combine")
@@ -479,7 +490,7 @@ class EPEngine:
             dgu, act_w, parts = gemm.bwd_gradact(dyperm, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
                                                  units=units)
             self._mark("bwd:grad_act GEMM+dSwiGLU")
-            fused = self.is_cuda and FUSED_COMBINE
+            fused = self.is_cuda and use_fused_combine(W_down.shape[2], w.size, True)
             if fused:
                 dxperm = None
                 gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units, push=self._push_target(h, offs))
@@ -518,7 +529,7 @@ class EPEngine:
                 self._mark("bwd:combine reduce (push overlapped)")
                 return dx, gtw, dW_gateup, dW_down
         del dgu, act_w
-        if dxperm is None and self.is_cuda and FUSED_COMBINE and not USE_TMA_GATHER:
+        if dxperm is None and self.is_cuda and not USE_TMA_GATHER:
             # weight gradients were enqueued after the push so they overlap the other ranks' pushes
             yield ("barrier",)
             self._mark("bwd:combine barrier")

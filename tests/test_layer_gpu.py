@@ -45,6 +45,16 @@ def test_virtual_cluster_gpu_matches_oracle(N, T, H, I, E, K):
     compare(res, oracle(prob), 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("mode", ["0", "1"])
+def test_virtual_cluster_fused_and_separate_combine(mode, monkeypatch):
+    """Both combine paths (rows pushed from the GEMM epilogue / separate combine_push kernel) on 4 emulated ranks."""
+    from teramoe_b200 import engine
+    monkeypatch.setattr(engine, "_FUSED_MODE", mode)
+    prob = make_problem(4, 260, 512, 256, 16, 4, seed=21, dtype=torch.bfloat16, device="cuda", x_scale=0.5, w_scale=0.05, drop_some=True,
+                        empty_expert=3, uneven_tokens=True)
+    compare(run_virtual(prob, "cuda"), oracle(prob), 2e-2, 2e-2)
+
+
 def test_ep1_public_api_autograd_and_determinism():
     # reference accuracy protocol: x ~ 0.1 N(0,1), W ~ 0.02 N(0,1); limits max_abs 1e-2, calc_diff 1e-5, cosine 0.99
     prob = make_problem(1, 512, 1024, 1024, 16, 8, seed=42, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02)
