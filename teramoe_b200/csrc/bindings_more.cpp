@@ -7,6 +7,7 @@
 #include <torch/extension.h>
 
 #include "comm.h"
+#include "fused.h"
 #include "launch_count.h"
 #include "routing.h"
 #include "runtime.h"
@@ -38,6 +39,7 @@ void* bf16(const torch::Tensor& t, const char* name) {
     TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.is_contiguous(), name, " must be a contiguous bf16 CUDA tensor");
     return t.data_ptr();
 }
+void check_i32(const torch::Tensor& t, const char* name) { (void)i32(t, name); }
 int* opt_status(const c10::optional<torch::Tensor>& s) { return s.has_value() ? i32(*s, "status") : nullptr; }
 
 struct TopK {
@@ -51,7 +53,7 @@ TopK topk(const torch::Tensor& idx) {
 }
 
 tmoe::LayoutOut layout_out(const std::vector<torch::Tensor>& t) {
-    TORCH_CHECK(t.size() == 8, "layout tensor list must have 8 entries");
+    TORCH_CHECK(t.size() == 9, "layout tensor list must have 9 entries");
     tmoe::LayoutOut o;
     o.expert_total = i32(t[0], "expert_total");
     o.my_src_off = i32(t[1], "my_src_off");
@@ -61,6 +63,8 @@ tmoe::LayoutOut layout_out(const std::vector<torch::Tensor>& t) {
     o.seg_offsets = i32(t[5], "seg_offsets");
     o.num_mblocks = i32(t[6], "num_mblocks");
     o.sizes = i32(t[7], "sizes");
+    o.send_base = i32(t[8], "send_base");
+    TORCH_CHECK(t[6].numel() >= 2, "num_mblocks must hold 2 ints");
     return o;
 }
 
@@ -103,12 +107,88 @@ void slot_pad_fill(torch::Tensor seg_offsets, torch::Tensor expert_total_local, 
 }
 
 void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_base, std::vector<torch::Tensor> layout,
-                  torch::Tensor send_slot, torch::Tensor send_row, torch::Tensor land_off, torch::Tensor ndst) {
+                  torch::Tensor send_slot, torch::Tensor send_row, torch::Tensor land_off, torch::Tensor ndst,
+                  c10::optional<torch::Tensor> send_order) {
     const TopK tk = topk(topk_idx);
     c10::cuda::CUDAGuard guard(topk_idx.device());
     TM_CHECK_CUDA(tmoe::route_assign(tk.ptr, tk.is64, tk.T, tk.K, (int)E, (int)N, i32(chunk_base, "chunk_base"), layout_out(layout),
                                      i32(send_slot, "send_slot"), i32(send_row, "send_row"), i32(land_off, "land_off"),
-                                     i32(ndst, "ndst"), cur_stream()));
+                                     i32(ndst, "ndst"), send_order.has_value() ? i32(*send_order, "send_order") : nullptr, cur_stream()));
+}
+
+void arrival_order(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, int64_t groups, torch::Tensor seg_offsets, torch::Tensor unit_blk,
+                   torch::Tensor num_units, torch::Tensor blk_group, torch::Tensor unit_order) {
+    c10::cuda::CUDAGuard guard(meta.device());
+    TM_CHECK_CUDA(tmoe::arrival_order(i32(meta, "meta"), (int)rank, (int)N, (int)E, (int)groups, i32(seg_offsets, "seg_offsets"),
+                                      i32(unit_blk, "unit_blk"), i32(num_units, "num_units"), (int)unit_blk.numel() - 1,
+                                      i32(blk_group, "blk_group"), i32(unit_order, "unit_order"), cur_stream()));
+}
+
+void zero_pad_rows(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_x) {
+    c10::cuda::CUDAGuard guard(slot_x.device());
+    TM_CHECK_CUDA(tmoe::zero_pad_rows(i32(seg_offsets, "seg_offsets"), i32(expert_total_local, "expert_total_local"),
+                                      (int)expert_total_local.numel(), bf16(slot_x, "slot_x"), (int)slot_x.size(1), cur_stream()));
+}
+
+// Fused dispatch + GEMM.  kind 0 forward (gate_up + SwiGLU), 1 backward (grad_act + dSwiGLU).
+//   gemm_t : [slot_x view, weights, row_w, out0, out1] (+ [preact, droute_part] for kind 1)
+//   layout : [mblock_expert, num_mblocks, unit_blk, num_units]
+//   send_t : [x, topk_idx, send_order, num_send, send_slot, send_row] (+ [topk_w] when with_meta)
+//   sym_t  : [arena_ptrs, ctrl_ptrs, blk_cnt view, unit_order, seg_offsets, expert_total_local]
+//   offs   : [slot_x, slot_w, slot_tk, slot_row, row_first, blk_cnt(control arena)]
+void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout,
+                         std::vector<torch::Tensor> send_t, std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, int64_t E,
+                         int64_t N, bool with_meta, int64_t num_dispatch_clusters, c10::optional<torch::Tensor> status, int64_t num_sms) {
+    TORCH_CHECK(gemm_t.size() == (kind == 0 ? 5u : 7u) && layout.size() == 4 && send_t.size() == (with_meta ? 7u : 6u) &&
+                sym_t.size() == 6 && offs.size() == 6, "fused_dispatch_gemm: wrong argument lists");
+    const torch::Tensor& slot_x = gemm_t[0];
+    const torch::Tensor& w = gemm_t[1];
+    const int S = (int)slot_x.size(0), H = (int)slot_x.size(1);
+    tmoe::GemmArgsPublic p{};
+    check_i32(layout[0], "mblock_expert");
+    p.lay.mblock_expert = layout[0].data_ptr<int>();
+    p.lay.num_mblocks_dev = i32(layout[1], "num_mblocks");
+    p.lay.max_mblocks = S / 128;
+    p.lay.unit_blk = i32(layout[2], "unit_blk");
+    p.lay.num_units_dev = i32(layout[3], "num_units");
+    p.lay.max_units = (int)layout[2].numel() - 1;
+    p.H = H;
+    p.num_local_experts = (int)w.size(0);
+    p.I = kind == 0 ? (int)w.size(1) / 2 : (int)w.size(2);
+    p.row_w = f32(gemm_t[2], "row_w");
+    p.out0 = bf16(gemm_t[3], "out0");
+    p.out1 = bf16(gemm_t[4], "out1");
+    if (kind == 1) {
+        p.preact = bf16(gemm_t[5], "preact");
+        p.droute_part = f32(gemm_t[6], "droute_part");
+    }
+    p.status = opt_status(status);
+    const TopK tk = topk(send_t[1]);
+    tmoe::FusedArgs f{};
+    f.num_dispatch_clusters = (int)num_dispatch_clusters;
+    f.x = bf16(send_t[0], "x");
+    f.topk_idx = tk.ptr;
+    f.idx_is64 = tk.is64;
+    f.send_order = i32(send_t[2], "send_order");
+    f.num_send = i32(send_t[3], "num_send");
+    f.max_send = (int)send_t[2].numel();
+    f.send_slot = i32(send_t[4], "send_slot");
+    f.send_row = i32(send_t[5], "send_row");
+    f.topk_w = with_meta ? f32(send_t[6], "topk_w") : nullptr;
+    f.T = tk.T; f.K = tk.K; f.H = H; f.E = (int)E; f.N = (int)N;
+    f.with_meta = with_meta ? 1 : 0;
+    f.slot_cap = S;
+    f.arena_ptrs = u64(sym_t[0], "arena_ptrs");
+    f.ctrl_ptrs = u64(sym_t[1], "ctrl_ptrs");
+    f.blk_cnt = i32(sym_t[2], "blk_cnt");
+    f.unit_order = i32(sym_t[3], "unit_order");
+    f.seg_offsets = i32(sym_t[4], "seg_offsets");
+    f.expert_total_local = i32(sym_t[5], "expert_total_local");
+    f.off_slot_x = offs[0]; f.off_slot_w = offs[1]; f.off_slot_tk = offs[2]; f.off_slot_row = offs[3]; f.off_row_first = offs[4];
+    f.off_blk_cnt = offs[5];
+    TORCH_CHECK(send_t[0].size(1) == H && S % 128 == 0 && sym_t[2].numel() >= S / 128, "fused_dispatch_gemm: shape mismatch");
+    c10::cuda::CUDAGuard guard(slot_x.device());
+    TM_CHECK_CUDA(tmoe::fused_dispatch_gemm((int)kind, bf16(slot_x, "slot_x"), S, bf16(w, "weights"), p, f, (int)num_sms, cur_stream()));
 }
 
 void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site,
@@ -224,6 +304,9 @@ void register_more(pybind11::module_& m) {
     m.def("layout_finalize", &layout_finalize);
     m.def("slot_pad_fill", &slot_pad_fill);
     m.def("route_assign", &route_assign);
+    m.def("arrival_order", &arrival_order);
+    m.def("zero_pad_rows", &zero_pad_rows);
+    m.def("fused_dispatch_gemm", &fused_dispatch_gemm);
     m.def("ep_barrier", &ep_barrier);
     m.def("dispatch_push", &dispatch_push);
     m.def("expand_rows", &expand_rows);

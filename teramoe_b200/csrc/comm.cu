@@ -38,20 +38,6 @@ __global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, 
     }
 }
 
-// Warp-wide row copy (nvec 16-byte vectors) with four loads in flight per lane before the stores, so that
-// a warp keeps 2 KB outstanding instead of 512 bytes.
-__device__ __forceinline__ void warp_copy_row(int4* dst, const int4* src, int nvec, int lane) {
-    int i = lane;
-    for (; i + 96 < nvec; i += 128) {
-        const int4 a = src[i], b = src[i + 32], c = src[i + 64], d = src[i + 96];
-        st_na_v4(dst + i, a);
-        st_na_v4(dst + i + 32, b);
-        st_na_v4(dst + i + 64, c);
-        st_na_v4(dst + i + 96, d);
-    }
-    for (; i < nvec; i += 32) st_na_v4(dst + i, src[i]);
-}
-
 __device__ __forceinline__ int64_t load_topk(const void* idx, int is64, long i) {
     return is64 ? reinterpret_cast<const int64_t*>(idx)[i] : (int64_t) reinterpret_cast<const int32_t*>(idx)[i];
 }

@@ -1,0 +1,343 @@
+// Fused dispatch + grouped GEMM: ONE cooperative kernel in which a few CTA pairs push this rank's
+// routed rows straight into the peers' slot-space operand buffers over NVLink while all other CTA
+// pairs run the tcgen05 (cta_group::2) GEMM that consumes the rows arriving from the peers.
+//
+//   dispatch pairs   walk this rank's (token,k) entries in sending order (own rank first, then rank+1,
+//                    ... so that at any moment every rank receives from one sender), store each row
+//                    into slot `send_slot` of the destination's operand buffer (16-byte peer stores) and
+//                    then publish it: fence.acq_rel.sys + red.add on the destination's per-block arrival
+//                    counter.  In forward they also store the slot tables (route weight, entry id, row).
+//   compute pairs    the CTA-pair GEMM of gemm2.cu over the units sorted by arrival group; before the
+//                    first load of a tile the producer thread waits (bounded, ld.acquire.sys) until the
+//                    arrival counter of its 128-row block has reached the block's row count, then
+//                    fence.proxy.async, then TMA.  Weights never wait.
+//
+// Forward:  GU = Xslots . Wgu^T with the SwiGLU x route epilogue (pre-activation side store).
+// Backward: gA = dYslots . Wd with the dSwiGLU epilogue (dGU, act x route, route-gradient partials).
+//
+// Reference counterpart: the dispatch + compute roles of teramoe_fused_forward_kernel /
+// teramoe_fused_backward_kernel (csrc/teramoe/teramoe_orchestrator.cu:524-1369, :1626-1907, :2978-3042,
+// :4495-4848).  Differences: rows go to their final slot (no ring, no publisher warps, no scheduler SM:
+// the tile order is the static arrival order computed by arrival_order in routing.cu), readiness is
+// one counter per 128-row block, and every wait is bounded.
+#include "fused.h"
+
+#include "gemm_common.cuh"
+
+namespace tmoe {
+
+using namespace detail;
+
+namespace {
+
+constexpr int kStagesF = 6;
+constexpr int kBHalfBytesF = (BN / 2) * BK * 2;
+constexpr int kStageBytesF = kAStageBytes + kBHalfBytesF;       // 32 KB
+constexpr int kSmemBytesF = kStagesF * kStageBytesF + 1024 + 256;
+constexpr int kSuperUF = 8;
+
+struct TileF {
+    int blk0, two, n_blk, group;
+};
+
+__device__ __forceinline__ bool get_tile_f(const GemmArgs& g, const int* unit_order, int t, int num_units, TileF& tile) {
+    const int total = num_units * g.num_n_blocks;
+    if (t >= total) return false;
+    const int per_super = kSuperUF * g.num_n_blocks;
+    const int super = t / per_super;
+    const int r = t - super * per_super;
+    const int u_first = super * kSuperUF;
+    const int u_cnt = min(kSuperUF, num_units - u_first);
+    tile.n_blk = r / u_cnt;
+    const int u = unit_order[u_first + (r - tile.n_blk * u_cnt)];
+    tile.blk0 = g.unit_blk[u];
+    tile.two = (g.unit_blk[u + 1] - tile.blk0) == 2;
+    tile.group = g.mblock_expert[tile.blk0];
+    return true;
+}
+
+__device__ __forceinline__ long long load_idx(const void* idx, int is64, long i) {
+    return is64 ? reinterpret_cast<const long long*>(idx)[i] : (long long) reinterpret_cast<const int*>(idx)[i];
+}
+
+__device__ __forceinline__ void red_add_relaxed_sys(int* p, int v) {
+    asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           const __grid_constant__ GemmArgs g, const __grid_constant__ FusedArgs f) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bar_base = smem_base + kStagesF * kStageBytesF;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStagesF + s); };
+    auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * kStagesF + s); };
+    auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * kStagesF + 2 + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kStagesF * kStageBytesF + 8 * (2 * kStagesF + 4));
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const int cd = f.num_dispatch_clusters;
+    const bool is_dispatch = cluster_id < cd;
+
+    // Every CTA sets its barriers and tensor memory up the same way (tcgen05 alloc is collective over the pair).
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kStagesF; ++s) {
+            mbar_init(full_bar(s), 2);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(tfull_bar(s), 1);
+            mbar_init(tempty_bar(s), 2 * kEpiWarps);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 2) tmem_alloc_2cta(smem_u32((const void*)tmem_slot), kTmemCols);
+    tcgen05_fence_before();
+    cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (is_dispatch) {
+        // ------------------------------------------------------------------ dispatch role (all 12 warps)
+        const int num_send = min(*f.num_send, f.max_send);
+        const int warps_total = cd * 2 * (kThreads / 32);
+        const int wid = (cluster_id * 2 + (int)rank) * (kThreads / 32) + warp;
+        const int nvec = f.H / 8;
+        const int e_local = f.E / f.N;
+        for (int base = wid * 2; base < num_send; base += warps_total * 2) {
+            int blk[2] = {-1, -1};
+            int dst_rank[2] = {0, 0};
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int pos = base + q;
+                if (pos >= num_send) break;
+                const int entry = f.send_order[pos];
+                const int t = entry / f.K, k = entry - t * f.K;
+                const int e = (int)load_idx(f.topk_idx, f.idx_is64, entry);
+                const int d = e / e_local;
+                const int slot = f.send_slot[entry];
+                if (slot < 0 || slot >= f.slot_cap) continue;   // defensive: never store outside the destination table
+                const uint64_t arena = f.arena_ptrs[d];
+                warp_copy_row(reinterpret_cast<int4*>(arena + f.off_slot_x + (uint64_t)slot * f.H * 2),
+                                reinterpret_cast<const int4*>(static_cast<const __nv_bfloat16*>(f.x) + (long)t * f.H), nvec, lane);
+                if (f.with_meta && lane == 0) {
+                    const int row = f.send_row[(long)t * f.N + d];
+                    reinterpret_cast<float*>(arena + f.off_slot_w)[slot] = f.topk_w[entry];
+                    reinterpret_cast<int*>(arena + f.off_slot_tk)[slot] = entry;
+                    reinterpret_cast<int*>(arena + f.off_slot_row)[slot] = row;
+                    bool first = true;                       // first entry of token t that goes to rank d
+                    for (int k2 = 0; k2 < k; ++k2) {
+                        const long long e2 = load_idx(f.topk_idx, f.idx_is64, (long)t * f.K + k2);
+                        if (e2 >= 0 && e2 < f.E && (int)e2 / e_local == d) first = false;
+                    }
+                    if (first) reinterpret_cast<int*>(arena + f.off_row_first)[row] = slot;
+                }
+                blk[q] = slot >> 7;
+                dst_rank[q] = d;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                fence_acq_rel_sys();   // this warp's row and table stores are ordered before the arrival counts
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    if (blk[q] >= 0) red_add_relaxed_sys(reinterpret_cast<int*>(f.ctrl_ptrs[dst_rank[q]] + f.off_blk_cnt) + blk[q], 1);
+            }
+        }
+    } else {
+        const int cid = cluster_id - cd;
+        const int ncc = num_clusters - cd;
+        int num_units = g.max_units;
+        if (g.num_units_dev != nullptr) num_units = min(*g.num_units_dev, g.max_units);
+        const int nk = g.k_total / BK;
+
+        if (warp == 0) {
+            // -------------------------------------------------------------- TMA producer
+            if (elect_one()) {
+                int stage = 0;
+                uint32_t phase = 0;
+                bool ok = true;
+                TileF tile;
+                for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc) {
+                    const bool live = (rank == 0) || tile.two;
+                    const int my_blk = tile.blk0 + (int)rank;
+                    if (live) {
+                        // rows of this block come from the peers' dispatch pairs: wait for all of them
+                        const int le = g.mblock_expert[my_blk];
+                        const int valid_end = f.seg_offsets[le] + f.expert_total_local[le];
+                        const int need = max(0, min(128, valid_end - my_blk * 128));
+                        if (!wait_flag_ge_sys(f.blk_cnt + my_blk, need, g.status, 600)) { *abort_flag = 1u; ok = false; break; }
+                        fence_proxy_async_all();   // generic-proxy peer stores -> async-proxy (TMA) reads
+                    }
+                    const int m0 = my_blk * BM;
+                    const int n0 = tile.n_blk * BN + (int)rank * (BN / 2);
+                    for (int kb = 0; kb < nk; ++kb) {
+                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, g.status, 610)) { ok = false; break; }
+                        const uint32_t a_dst = smem_base + stage * kStageBytesF;
+                        const uint32_t b_dst = a_dst + kAStageBytes;
+                        const uint32_t bar = mapa_shared(full_bar(stage), 0);
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kStageBytesF);
+                        else mbar_arrive_cluster(bar);
+                        const int k = kb * BK;
+                        tma_load_2d_2cta(a_dst, &map_a, bar, k, m0);
+                        if constexpr (!B_MN) {
+                            tma_load_2d_2cta(b_dst, &map_b, bar, k, tile.group * g.b_group_rows + n0);
+                        } else {
+                            const int krow = tile.group * g.b_group_rows + k;
+#pragma unroll
+                            for (int a = 0; a < BN / 128; ++a) tma_load_2d_2cta(b_dst + a * kAtomBytes, &map_b, bar, n0 + 64 * a, krow);
+                        }
+                        if (++stage == kStagesF) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        } else if (warp == 1 && rank == 0) {
+            // -------------------------------------------------------------- UMMA issuer
+            constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, false, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            TileF tile;
+            int iter = 0;
+            for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc, ++iter) {
+                const int as = iter & 1;
+                const uint32_t aphase = (iter >> 1) & 1;
+                if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, 620)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+                for (int kb = 0; kb < nk; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, g.status, 621)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    if (elect_one()) {
+                        const uint32_t a_addr = smem_base + stage * kStageBytesF;
+                        const uint32_t b_addr = a_addr + kAStageBytes;
+#pragma unroll
+                        for (int k = 0; k < BK / UK; ++k) {
+                            const uint64_t a_desc = make_smem_desc_sw128(a_addr + k * (UK * 2), 0, 1024);
+                            const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_addr + k * (UK * 128), kAtomBytes, 1024)
+                                                         : make_smem_desc_sw128(b_addr + k * (UK * 2), 0, 1024);
+                            umma_bf16_ss_2cta(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                        umma_commit_2cta(empty_bar(stage), 3u);
+                        if (kb == nk - 1) umma_commit_2cta(tfull_bar(as), 3u);
+                    }
+                    __syncwarp();
+                    if (++stage == kStagesF) { stage = 0; phase ^= 1u; }
+                }
+            }
+        } else if (warp >= 4) {
+            // -------------------------------------------------------------- epilogue
+            const int q = warp & 3;
+            const int h = (warp - 4) >> 2;
+            const int r = q * 32 + lane;
+            bool ok = true;
+            TileF tile;
+            int iter = 0;
+            for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc, ++iter) {
+                const int as = iter & 1;
+                const uint32_t aphase = (iter >> 1) & 1;
+                if (!mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, 630)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * BN + h * (BN / 2));
+                const int n0 = tile.n_blk * BN + h * (BN / 2);
+                const bool live = (rank == 0) || tile.two;
+                const long row = (long)(tile.blk0 + (int)rank) * BM + r;
+                if (live) epilogue_thread<EPI>(g, taddr0, row, true, n0, tile.n_blk * 2 + h, false);
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(as), 0));
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 2) {
+        tcgen05_fence_after();
+        tmem_dealloc_2cta(tmem_base, kTmemCols);
+    }
+}
+
+template <bool B_MN, int EPI>
+cudaError_t launch_fused(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, const FusedArgs& f, int num_sms,
+                         cudaStream_t stream) {
+    auto kern = fused_dispatch_gemm_kernel<B_MN, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesF);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    int grid = num_sms & ~1;
+    if (grid < 2 * (f.num_dispatch_clusters + 1)) return cudaErrorInvalidConfiguration;
+    // All CTAs must be resident at once (compute pairs wait for rows that dispatch pairs of OTHER ranks send,
+    // and this rank's dispatch pairs serve the others): a cooperative launch makes the runtime check that.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytesF;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ma, mb, g, f);
+}
+
+}  // namespace
+
+cudaError_t fused_dispatch_gemm(int kind, const void* slot_x, int slot_rows, const void* w, const GemmArgsPublic& p, const FusedArgs& f,
+                                int num_sms, cudaStream_t stream) {
+    // kind 0: forward gate_up + SwiGLU (W_gateup [E*2I, H] K-major);  kind 1: backward grad_act + dSwiGLU (W_down [E*H, I] MN-major)
+    if (p.H % BK != 0 || p.I % 32 != 0 || slot_rows % BM != 0 || slot_rows <= 0) return cudaErrorInvalidValue;
+    CUtensorMap ma, mb;
+    cudaError_t e;
+    if ((e = make_map(&ma, slot_x, (uint64_t)slot_rows, p.H, BK, BM)) != cudaSuccess) return e;
+    GemmArgs g{};
+    g.k_total = p.H;
+    g.max_mblocks = slot_rows / BM;
+    g.num_mblocks_dev = p.lay.num_mblocks_dev;
+    g.mblock_expert = p.lay.mblock_expert;
+    g.unit_blk = p.lay.unit_blk;
+    g.num_units_dev = p.lay.num_units_dev;
+    g.max_units = p.lay.max_units;
+    g.row_w = p.row_w;
+    g.status = p.status;
+    const int sms = default_sms(num_sms);
+    if (kind == 0) {
+        if ((e = make_map(&mb, w, (uint64_t)p.num_local_experts * 2 * p.I, p.H, BK, BN / 2)) != cudaSuccess) return e;
+        g.n_total = 2 * p.I;
+        g.num_n_blocks = (2 * p.I + BN - 1) / BN;
+        g.b_group_rows = 2 * p.I;
+        g.d = static_cast<__nv_bfloat16*>(p.out0);      // act
+        g.ldd = p.I;
+        g.aux = static_cast<__nv_bfloat16*>(p.out1);    // preact
+        g.ld_aux = 2 * p.I;
+        return launch_fused<false, kEpiSwiGLU>(ma, mb, g, f, sms, stream);
+    }
+    if ((e = make_map(&mb, w, (uint64_t)p.num_local_experts * p.H, p.I, 64, BK)) != cudaSuccess) return e;
+    g.n_total = p.I;
+    g.num_n_blocks = (p.I + BN - 1) / BN;
+    g.b_group_rows = p.H;
+    g.d = static_cast<__nv_bfloat16*>(p.out0);          // act_w
+    g.ldd = p.I;
+    g.aux = static_cast<__nv_bfloat16*>(p.out1);        // dGU
+    g.ld_aux = 2 * p.I;
+    g.preact = static_cast<const __nv_bfloat16*>(p.preact);
+    g.droute_part = p.droute_part;
+    g.n_parts = 2 * ((p.I + BN - 1) / BN);
+    return launch_fused<true, kEpiDSwiGLU>(ma, mb, g, f, sms, stream);
+}
+
+}  // namespace tmoe

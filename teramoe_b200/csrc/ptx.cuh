@@ -350,6 +350,20 @@ __device__ __forceinline__ void st_na_v4(void* p, int4 v) {
                  : "memory");
 }
 
+// Warp-wide row copy (nvec 16-byte vectors) with four loads in flight per lane before the stores, so that
+// a warp keeps 2 KB outstanding instead of 512 bytes.
+__device__ __forceinline__ void warp_copy_row(int4* dst, const int4* src, int nvec, int lane) {
+    int i = lane;
+    for (; i + 96 < nvec; i += 128) {
+        const int4 a = src[i], b = src[i + 32], c = src[i + 64], d = src[i + 96];
+        st_na_v4(dst + i, a);
+        st_na_v4(dst + i + 32, b);
+        st_na_v4(dst + i + 64, c);
+        st_na_v4(dst + i + 96, d);
+    }
+    for (; i < nvec; i += 32) st_na_v4(dst + i, src[i]);
+}
+
 // Bounded wait until *flag >= target (acquire, system scope).  One thread calls it.
 __device__ __forceinline__ bool wait_flag_ge_sys(const int* flag, int target, int* status, int site,
                                                  uint64_t limit_ns = TMOE_WAIT_LIMIT_NS) {

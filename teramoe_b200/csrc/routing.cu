@@ -19,6 +19,8 @@
 // atomicAdd slot claim at csrc/teramoe/teramoe_orchestrator.cu:1238-1259, which this replaces.
 #include "routing.h"
 
+#include <cuda_bf16.h>
+
 #include "ptx.cuh"
 
 namespace tmoe {
@@ -143,6 +145,17 @@ layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, Lay
         o.sizes[7] = tmax;
         o.num_mblocks[0] = my_spad / 128;
         o.seg_offsets[e_local] = my_spad;
+        // send order of a fused dispatch: destination ranks in rotation starting with this rank
+        int run = 0;
+        for (int p = 0; p < N; ++p) {
+            const int d = (rank + p) % N;
+            for (int le = 0; le < e_local; ++le) {
+                const int e = d * e_local + le;
+                o.send_base[e] = run;
+                run += meta[rank * C + e];
+            }
+        }
+        o.num_mblocks[1] = run;
     }
     // this rank's segment table
     for (int le = threadIdx.x; le < e_local; le += blockDim.x) o.seg_offsets[le] = o.seg_off_all[rank * e_local + le];
@@ -188,7 +201,8 @@ slot_pad_fill_kernel(const int* seg_offsets, const int* expert_total_local, int 
 // (warp, k, lane) order.  run[] lives in shared memory and starts from the chunk's scanned base.
 __global__ void __launch_bounds__(kChunkTokens)
 route_assign_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, LayoutOut o,
-                    int* send_slot /* [T,K] */, int* send_row /* [T,N] */, int* land_off /* [T] */, int* ndst /* [T] */) {
+                    int* send_slot /* [T,K] */, int* send_row /* [T,N] */, int* land_off /* [T] */, int* ndst /* [T] */,
+                    int* send_order /* [T*K] or null */) {
     extern __shared__ int run[];
     const int C = E + N + 2;
     const int e_local = E / N;
@@ -207,8 +221,10 @@ route_assign_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, 
                 int slot = -1;
                 if (e >= 0) {
                     const int base = run[e];
-                    slot = o.seg_off_all[e] + o.my_src_off[e] + base + __popc(same & lt);
+                    const int j = base + __popc(same & lt);
+                    slot = o.seg_off_all[e] + o.my_src_off[e] + j;
                     mask |= 1u << (e / e_local);
+                    if (send_order != nullptr) send_order[o.send_base[e] + j] = t * K + k;
                 }
                 __syncwarp();
                 if (e >= 0 && (same & lt) == 0) run[e] += __popc(same);
@@ -276,11 +292,82 @@ cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local,
 }
 
 cudaError_t route_assign(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, const LayoutOut& out,
-                         int* send_slot, int* send_row, int* land_off, int* ndst, cudaStream_t stream) {
+                         int* send_slot, int* send_row, int* land_off, int* ndst, int* send_order, cudaStream_t stream) {
     const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
     if (chunks == 0) return cudaSuccess;
     route_assign_kernel<<<chunks, kChunkTokens, (E + N + 2) * sizeof(int), stream>>>(topk_idx, is64, T, K, E, N, chunk_base, out,
-                                                                                  send_slot, send_row, land_off, ndst);
+                                                                                  send_slot, send_row, land_off, ndst, send_order);
+    return cudaGetLastError();
+}
+
+namespace {
+// One block.  Per 128-row block: the arrival group of the latest source that owns rows in it (source s
+// reaches this rank in phase (rank - s) mod N of its rotation; phases are binned into `groups`); then
+// the units sorted by group.
+__global__ void __launch_bounds__(256)
+arrival_order_kernel(const int* meta, int rank, int N, int E, int groups, const int* seg_offsets, const int* unit_blk,
+                     const int* num_units_p, int max_units, int* blk_group, int* unit_order) {
+    const int C = E + N + 2;
+    const int e_local = E / N;
+    for (int le = threadIdx.x; le < e_local; le += blockDim.x) {
+        const int e = rank * e_local + le;
+        const int b0 = seg_offsets[le] / 128, b1 = seg_offsets[le + 1] / 128;
+        for (int b = b0; b < b1; ++b) {
+            const int lo = (b - b0) * 128, hi = lo + 128;
+            int cum = 0, grp = 0;
+            for (int s = 0; s < N; ++s) {
+                const int c = meta[s * C + e];
+                if (c > 0 && cum < hi && cum + c > lo) {
+                    const int phase = (rank - s + N) % N;
+                    grp = max(grp, phase * groups / N);
+                }
+                cum += c;
+            }
+            blk_group[b] = grp;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int nu = min(num_units_p[0], max_units);
+        int pos = 0;
+        for (int gsel = 0; gsel < groups; ++gsel)
+            for (int u = 0; u < nu; ++u) {
+                const int b = unit_blk[u];
+                int gu = blk_group[b];
+                if (unit_blk[u + 1] - b == 2) gu = max(gu, blk_group[b + 1]);
+                if (gu == gsel) unit_order[pos++] = u;
+            }
+    }
+}
+}  // namespace
+
+namespace {
+// Pad rows of the slot-space operand table must read as zeros (they take part in the weight gradients).
+__global__ void __launch_bounds__(256)
+zero_pad_rows_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, __nv_bfloat16* slot_x, int H) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int le = blockIdx.x; le < e_local; le += gridDim.x) {
+        const int first = seg_offsets[le] + expert_total_local[le];
+        const int last = seg_offsets[le + 1];
+        for (int s = first + warp; s < last; s += blockDim.x / 32) {
+            int4* row = reinterpret_cast<int4*>(slot_x + (long)s * H);
+            for (int i = lane; i < H / 8; i += 32) row[i] = make_int4(0, 0, 0, 0);
+        }
+    }
+}
+}  // namespace
+
+cudaError_t zero_pad_rows(const int* seg_offsets, const int* expert_total_local, int e_local, void* slot_x, int H, cudaStream_t stream) {
+    if (e_local <= 0) return cudaSuccess;
+    zero_pad_rows_kernel<<<e_local < 512 ? e_local : 512, 256, 0, stream>>>(seg_offsets, expert_total_local, e_local,
+                                                                            static_cast<__nv_bfloat16*>(slot_x), H);
+    return cudaGetLastError();
+}
+
+cudaError_t arrival_order(const int* meta, int rank, int N, int E, int groups, const int* seg_offsets, const int* unit_blk,
+                          const int* num_units, int max_units, int* blk_group, int* unit_order, cudaStream_t stream) {
+    arrival_order_kernel<<<1, 256, 0, stream>>>(meta, rank, N, E, groups, seg_offsets, unit_blk, num_units, max_units, blk_group,
+                                                unit_order);
     return cudaGetLastError();
 }
 

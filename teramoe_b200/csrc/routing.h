@@ -13,7 +13,8 @@ struct LayoutOut {
     int* my_row_base;    // [N]   first row of this source's block in rank d's receive buffer
     int* recv_row_base;  // [N+1] this rank's receive buffer: first row of source s (last = total rows)
     int* seg_offsets;    // [El+1] this rank's padded segment offsets (rows of slot space)
-    int* num_mblocks;    // [1]
+    int* num_mblocks;    // [2]   live 128-row blocks of this rank; number of (token,k) entries this rank sends
+    int* send_base;      // [E]   position of this rank's first entry for expert e in its send order
     int* sizes;          // [8]   rows, padded slots, landing rows of this rank; their maxima over ranks; blocks; max tokens
 };
 
@@ -25,7 +26,16 @@ cudaError_t route_scan(const int* chunk_hist, int* chunk_base, int num_chunks, i
 cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const LayoutOut& out, cudaStream_t stream);
 cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w,
                           int* slot_tk, int* mblock_expert, int* unit_blk, int* num_units, cudaStream_t stream);
+// send_order (optional, [T*K]): entries (t*K+k) of this rank in the order a fused dispatch sends them:
+// destination ranks in rotation (own rank first, then rank+1, ...), experts ascending, ranks ascending.
 cudaError_t route_assign(const void* topk_idx, int is64, int T, int K, int E, int N, const int* chunk_base, const LayoutOut& out,
-                         int* send_slot, int* send_row, int* land_off, int* ndst, cudaStream_t stream);
+                         int* send_slot, int* send_row, int* land_off, int* ndst, int* send_order, cudaStream_t stream);
+
+cudaError_t zero_pad_rows(const int* seg_offsets, const int* expert_total_local, int e_local, void* slot_x, int H, cudaStream_t stream);
+
+// Arrival order for a fused dispatch + GEMM: blk_group[b] = latest arrival group (0..groups-1) among the
+// sources of block b; unit_order = units of the CTA-pair GEMM sorted by arrival group (stable).
+cudaError_t arrival_order(const int* meta, int rank, int N, int E, int groups, const int* seg_offsets, const int* unit_blk,
+                          const int* num_units, int max_units, int* blk_group, int* unit_order, cudaStream_t stream);
 
 }  // namespace tmoe

@@ -65,6 +65,22 @@ OVERLAP_BWD_COMBINE = os.environ.get("TERAMOE_OVERLAP_BWD_COMBINE", "0") == "1"
 OVERLAP_COMM_SMS = int(os.environ.get("TERAMOE_OVERLAP_COMM_SMS", "8"))
 
 TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw")
+EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operand rows, first slot of every received row
+
+# Dispatch fused into the GEMM that consumes it (csrc/fused.cu): one cooperative kernel, a few CTA pairs
+# push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
+# rows that arrive.  Used when the CTA-pair kernels are on and the GEMM outlasts the transfer.
+_FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "0")
+FUSED_DISPATCH_CLUSTERS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "6"))
+FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
+
+
+def use_fused_dispatch(I: int, num_ranks: int) -> bool:
+    if not USE_CTA_PAIRS or USE_TMA_GATHER:
+        return False
+    if _FUSED_DISPATCH_MODE in ("0", "1"):
+        return _FUSED_DISPATCH_MODE == "1"
+    return I >= 1536
 
 
 @dataclass
@@ -89,6 +105,10 @@ class LayerHandle:
     mblock_expert: torch.Tensor
     num_mblocks: torch.Tensor
     expert_total_local: torch.Tensor
+    send_order: Optional[torch.Tensor] = None    # fused dispatch: this rank's entries in sending order
+    num_send: Optional[torch.Tensor] = None      # device scalar: number of entries in send_order
+    unit_order: Optional[torch.Tensor] = None    # fused dispatch: units sorted by arrival group
+    fused_dispatch: bool = False
     unit_blk: Optional[torch.Tensor] = None      # CTA-pair GEMMs: first block of every unit (+ sentinel)
     num_units: Optional[torch.Tensor] = None
     slot_row: Optional[torch.Tensor] = None
@@ -109,16 +129,18 @@ class SavedForBackward:
     stats: dict = field(default_factory=dict)
 
 
-def _arena_geometry(maxima, H: int, K: int):
+def _arena_geometry(maxima, H: int, K: int, fused_dispatch: bool = False):
     rmax, smax, lmax, tmax = [max(int(v), 1) for v in maxima]
     lmax = max(lmax, tmax * K)      # the fused combine lands one row per (token, k) entry
+    smax = (smax + 127) // 128 * 128
     sizes = {
         "recv_x": rmax * H * 2, "slot_row": smax * 4, "slot_w": smax * 4, "slot_tk": smax * 4,
         "row_tok": rmax * 4, "row_land": rmax * 4, "row_slots": rmax * K * 4,
         "landing": lmax * H * 2, "gtw": tmax * K * 4,
+        "slot_x": smax * H * 2, "row_first": rmax * 4,
     }
     offs, off = {}, 0
-    for name in TABLES:
+    for name in TABLES + (EXTRA_TABLES if fused_dispatch else ()):
         offs[name] = off
         off += _round_up(sizes[name])
     return offs, off, (rmax, smax, lmax, tmax)
@@ -180,6 +202,8 @@ class EPEngine:
                 "row_slots": v(offs["row_slots"], [rmax, K], torch.int32),
                 "landing": v(offs["landing"], [lmax, H], torch.bfloat16),
                 "gtw": v(offs["gtw"], [tmax * K], torch.float32),
+                **({"slot_x": v(offs["slot_x"], [smax, H], torch.bfloat16),
+                    "row_first": v(offs["row_first"], [rmax], torch.int32)} if "slot_x" in offs else {}),
             }
         t = w.cpu_tables
         shapes = {"recv_x": ((rmax, H), dtype), "slot_row": ((smax,), torch.int32), "slot_w": ((smax,), torch.float32),
@@ -228,24 +252,28 @@ class EPEngine:
         yield ("barrier",)
         i32 = dict(dtype=torch.int32, device=dev)
         lay = [torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(N, **i32),
-               torch.empty(N + 1, **i32), torch.empty(El + 1, **i32), torch.empty(1, **i32), torch.empty(8, **i32)]
+               torch.empty(N + 1, **i32), torch.empty(El + 1, **i32), torch.empty(2, **i32), torch.empty(8, **i32),
+               torch.empty(E, **i32)]
         ext.layout_finalize(w.meta_view(C), rank, N, E, lay)
         w.sizes_host.copy_(lay[7], non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()
         w.check_status()
         R, S, Lr, rmax, smax, lmax, nmb, tmax = w.sizes_host.tolist()
         send_slot = torch.empty(T, K, **i32)
+        send_order = torch.empty(max(T * K, 1), **i32)
         send_row = torch.empty(T, N, **i32)
         land_off = torch.empty(T, **i32)
         ndst = torch.empty(T, **i32)
         if T > 0:
-            ext.route_assign(topk_idx, E, N, chunk_base, lay, send_slot, send_row, land_off, ndst)
+            ext.route_assign(topk_idx, E, N, chunk_base, lay, send_slot, send_row, land_off, ndst, send_order)
         mblock_expert = torch.empty(max(nmb, 1), **i32)
         unit_blk = torch.zeros((nmb + El) // 2 + 2, **i32)
         num_units = torch.zeros(1, **i32)
         h = LayerHandle(T, K, 0, E, N, rank, R, S, Lr, (rmax, smax, lmax, tmax), send_slot, send_row, land_off, ndst, lay[4], lay[5],
                         mblock_expert, lay[6], lay[0].view(N, El)[rank].contiguous(), topk_idx=topk_idx)
         h.unit_blk, h.num_units = unit_blk, num_units
+        h.send_order, h.num_send = send_order, lay[6][1:2]
+        h.num_mblocks = lay[6][0:1]
         return h
 
     def dispatch_gen(self, h: LayerHandle, x: torch.Tensor, topk_weights: Optional[torch.Tensor], with_meta: bool):
@@ -428,14 +456,28 @@ class EPEngine:
         h = yield from self.layout_gen(topk_idx, num_experts)
         self._mark("fwd:routing+layout")
         h.topk_weights = topk_weights
-        tabs, offs = yield from self.dispatch_gen(h, x, topk_weights, with_meta=True)
-        self._mark("fwd:dispatch (rest)")
-        self.snapshot_tables(h, tabs)
-        saved_x = tabs["recv_x"][:h.rows].clone()
-        self._mark("fwd:save tables and X")
         st = w.status if self.is_cuda else None
         units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
-        if USE_TMA_GATHER:
+        h.fused_dispatch = bool(self.is_cuda and use_fused_dispatch(I, w.size) and use_fused_combine(I, w.size, False)
+                                and use_fused_combine(I, w.size, True))
+        if h.fused_dispatch:
+            tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms)
+            self._mark("fwd:dispatch + gate_up GEMM (one kernel)")
+            R, S = h.rows, h.slots
+            h.slot_row, h.slot_w, h.slot_tk = tabs["slot_row"][:S].clone(), tabs["slot_w"][:S].clone(), tabs["slot_tk"][:S].clone()
+            saved_x = torch.empty(R, H, dtype=x.dtype, device=x.device)
+            if R > 0:
+                self.ext.expand_rows(tabs["slot_x"], tabs["row_first"], saved_x, R)     # one slot per received token
+            self._mark("fwd:save tables and X")
+        else:
+            tabs, offs = yield from self.dispatch_gen(h, x, topk_weights, with_meta=True)
+            self._mark("fwd:dispatch (rest)")
+            self.snapshot_tables(h, tabs)
+            saved_x = tabs["recv_x"][:h.rows].clone()
+            self._mark("fwd:save tables and X")
+        if h.fused_dispatch:
+            pass
+        elif USE_TMA_GATHER:
             act, preact = gemm.fwd_gateup(saved_x, W_gateup, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms, gather_rows=h.slot_row)
         else:
             xperm = self.expand(saved_x, h)
@@ -463,6 +505,49 @@ class EPEngine:
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
 
+    def fused_dispatch_gemm_gen(self, h: LayerHandle, rows_in, topk_weights, weights, kind: int, preact=None, num_sms=0):
+        """Dispatch fused with the GEMM that consumes it (csrc/fused.cu).  kind 0: forward, rows_in = x, weights =
+        W_gateup -> (act, preact); kind 1: backward, rows_in = grad_out, weights = W_down -> (act_w, dGU, route partials).
+        Also returns the table views and offsets of this call."""
+        w, ext = self.world, self.ext
+        T, H = rows_in.shape
+        K, N, E = h.K, h.N, h.E
+        h.H = H
+        I = weights.shape[1] // 2 if kind == 0 else weights.shape[2]
+        offs, total, maxima = _arena_geometry(h.maxima, H, K, True)
+        yield ("grow", total)
+        tabs = self._tables(offs, maxima, H, K, rows_in.dtype)
+        S = h.slots
+        dev = rows_in.device
+        if kind == 0:
+            ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert,
+                              h.unit_blk, h.num_units)
+            h.unit_order = torch.zeros(h.unit_blk.numel(), dtype=torch.int32, device=dev)
+            blk_group = torch.zeros(max(S // 128, 1), dtype=torch.int32, device=dev)
+            ext.arrival_order(w.meta_view(E + N + 2), h.rank, N, E, max(1, min(FUSED_DISPATCH_GROUPS, N)), h.seg_offsets, h.unit_blk,
+                              h.num_units, blk_group, h.unit_order)
+        ext.zero_pad_rows(h.seg_offsets, h.expert_total_local, tabs["slot_x"])
+        out0 = torch.empty(S, I, dtype=torch.bfloat16, device=dev)
+        out1 = torch.empty(S, 2 * I, dtype=torch.bfloat16, device=dev)
+        row_w = tabs["slot_w"] if kind == 0 else h.slot_w
+        if kind == 0:
+            gemm_t = [tabs["slot_x"], weights, row_w, out0, out1]
+            parts = None
+        else:
+            parts = torch.empty(S, gemm.num_droute_parts(I), dtype=torch.float32, device=dev)
+            gemm_t = [tabs["slot_x"], weights, row_w if S > 0 else torch.zeros(1, device=dev), out0, out1, preact, parts]
+        send_t = [rows_in, h.topk_idx, h.send_order, h.num_send, h.send_slot.view(-1), h.send_row]
+        if kind == 0:
+            send_t.append(topk_weights)
+        sym_t = [w.ptr_table(w.data, 0, "data"), w.ptr_table(w.control, 0, "control_base"), w.blk_cnt_view(), h.unit_order,
+                 h.seg_offsets, h.expert_total_local]
+        offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset]
+        ext.fused_dispatch_gemm(kind, gemm_t, [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units], send_t, sym_t, offsets, E, N,
+                                kind == 0, FUSED_DISPATCH_CLUSTERS, w.status, num_sms)
+        # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
+        w.blk_cnt_view()[: max(S // 128, 1)].zero_()
+        return tabs, offs, out0, out1, parts
+
     def _push_target(self, h: LayerHandle, offs):
         w = self.world
         return ([w.ptr_table(w.data, 0, "data"), h.slot_tk, h.slot_row, h.recv_row_base], offs["landing"])
@@ -473,9 +558,30 @@ class EPEngine:
         El = W_gateup.shape[0]
         st = w.status if self.is_cuda else None
         self._mark("bwd:start")
-        tabs, offs = yield from self.dispatch_gen(h, grad_out, None, with_meta=False)
-        self._mark("bwd:dispatch (rest)")
-        if USE_TMA_GATHER:
+        if h.fused_dispatch:
+            tabs, offs, act_w, dgu, parts = yield from self.fused_dispatch_gemm_gen(h, grad_out, None, W_down, 1, preact=saved.preact,
+                                                                                    num_sms=num_sms)
+            self._mark("bwd:dispatch + grad_act GEMM (one kernel)")
+            units = (h.unit_blk, h.num_units)
+            dyperm = tabs["slot_x"][: h.slots]
+            dxperm = None
+            gemm.bwd_dx(dgu, W_gateup, h.mblock_expert, h.num_mblocks, st, num_sms, units=units, push=self._push_target(h, offs))
+            if h.slots > 0:
+                self.ext.droute_push(parts, h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"), offs["gtw"])
+            self._mark("bwd:dX GEMM + pushed combine")
+            dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms, cta_pairs=True)
+            self._mark("bwd:dW_down GEMM")
+            xperm = self.expand(saved.saved_x, h)
+            self._mark("bwd:expand X")
+            dW_gateup = gemm.wgrad(dgu, xperm, h.seg_offsets, El, st, num_sms, cta_pairs=True)
+            self._mark("bwd:dW_gateup GEMM")
+            del xperm, dyperm
+        else:
+            tabs, offs = yield from self.dispatch_gen(h, grad_out, None, with_meta=False)
+            self._mark("bwd:dispatch (rest)")
+        if h.fused_dispatch:
+            pass
+        elif USE_TMA_GATHER:
             dy_rows = tabs["recv_x"]      # token-once rows of grad_out, read through h.slot_row by the GEMMs
             dgu, act_w, parts = gemm.bwd_gradact(dy_rows, W_down, saved.preact, h.slot_w, h.mblock_expert, h.num_mblocks, st, num_sms,
                                                  gather_rows=h.slot_row)
@@ -507,12 +613,13 @@ class EPEngine:
                 ev.record(main)
                 with torch.cuda.stream(side):
                     side.wait_event(ev)
-                    self._combine_push(h, dxperm, offs, parts, num_blocks=OVERLAP_COMM_SMS * 8)
+                    self._combine_push(h, dxperm, offs, parts, num_blocks=OVERLAP_COMM_SMS * 8)   # 0 = full grid
                     yield ("barrier",)                       # the barrier kernel goes to the side stream too
                     pushed = torch.cuda.Event()
                     pushed.record(side)
-                total = int((impl or {}).get("total_sms", 0)) or torch.cuda.get_device_properties(dyperm.device).multi_processor_count
-                num_sms = max(2, (total - OVERLAP_COMM_SMS) & ~1)
+                if OVERLAP_COMM_SMS > 0:
+                    total = int((impl or {}).get("total_sms", 0)) or torch.cuda.get_device_properties(dyperm.device).multi_processor_count
+                    num_sms = max(2, (total - OVERLAP_COMM_SMS) & ~1)
             dW_down = gemm.wgrad(dyperm, act_w, h.seg_offsets, El, st, num_sms, cta_pairs=pairs)
             del dyperm
             self._mark("bwd:dW_down GEMM")

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 CONTROL_ROW_INTS = 8192          # capacity of one metadata row (E + ranks + 2 ints must fit)
+MAX_BLOCKS = 65536               # per-block arrival counters of the fused dispatch (8.4 M slot rows)
 _ALIGN = 256
 
 
@@ -51,8 +52,9 @@ class EPWorld:
         if self.is_cuda:
             from .._build import load_ext
             self.ext = load_ext()
-            self.control_bytes = _round_up(size * CONTROL_ROW_INTS * 4 + 4096)
             self.signal_offset = size * CONTROL_ROW_INTS * 4
+            self.blk_cnt_offset = self.signal_offset + 1024
+            self.control_bytes = _round_up(self.blk_cnt_offset + MAX_BLOCKS * 4 + 4096)
             with torch.cuda.device(self.device):
                 self.control = self.ext.SymmetricArena(rank, size, self.control_bytes)
             self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -93,6 +95,9 @@ class EPWorld:
             t = torch.tensor([p + offset for p in arena.peer_ptrs()], dtype=torch.int64, device=self.device)
             self._ptr_cache[k] = t
         return t
+
+    def blk_cnt_view(self) -> torch.Tensor:
+        return self.control.view(self.blk_cnt_offset, [MAX_BLOCKS], torch.int32)
 
     def meta_view(self, C: int) -> torch.Tensor:
         return self.control.view(0, [self.size * C], torch.int32)
