@@ -3,10 +3,11 @@
 // pairs run the tcgen05 (cta_group::2) GEMM that consumes the rows arriving from the peers.
 //
 //   dispatch pairs   walk this rank's (token,k) entries in sending order (own rank first, then rank+1,
-//                    ... so that at any moment every rank receives from one sender), store each row
-//                    into slot `send_slot` of the destination's operand buffer (16-byte peer stores) and
-//                    then publish it: fence.acq_rel.sys + red.add on the destination's per-block arrival
-//                    counter.  In forward they also store the slot tables (route weight, entry id, row).
+//                    ... so that at any moment every rank receives from one sender), copy each row
+//                    into slot `send_slot` of the destination's operand buffer (bulk copies staged in
+//                    shared memory, one row in flight per warp) and then publish it: bulk-group wait,
+//                    fence.acq_rel.sys + red.add on the destination's per-block arrival counter.
+//                    In forward they also store the slot tables (route weight, entry id, row).
 //   compute pairs    the CTA-pair GEMM of gemm2.cu over the units sorted by arrival group; before the
 //                    first load of a tile the producer thread waits (bounded, ld.acquire.sys) until the
 //                    arrival counter of its 128-row block has reached the block's row count, then
@@ -33,8 +34,11 @@ namespace {
 constexpr int kStagesF = 6;
 constexpr int kBHalfBytesF = (BN / 2) * BK * 2;
 constexpr int kStageBytesF = kAStageBytes + kBHalfBytesF;       // 32 KB
-constexpr int kSmemBytesF = kStagesF * kStageBytesF + 1024 + 256;
+constexpr int kSmemBytesF = kStagesF * kStageBytesF + 1024 + 512;
 constexpr int kSuperUF = 8;
+constexpr int kDispatchChunk = 8192;                            // two per dispatch warp; 12 warps fill the six operand stages
+constexpr int kPublishBatch = 4;                                // rows published per system-scope fence
+static_assert((kThreads / 32) * 2 * kDispatchChunk <= kStagesF * kStageBytesF, "dispatch staging exceeds the operand stages");
 
 struct TileF {
     int blk0, two, n_blk, group;
@@ -78,6 +82,7 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * kStagesF + 2 + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kStagesF * kStageBytesF + 8 * (2 * kStagesF + 4));
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    auto dispatch_bar = [&](int w, uint32_t b) { return bar_base + 144u + 8u * (2u * w + b); };   // two per dispatch warp, after the flags
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -98,6 +103,10 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             mbar_init(tfull_bar(s), 1);
             mbar_init(tempty_bar(s), 2 * kEpiWarps);
         }
+        for (int w = 0; w < kThreads / 32; ++w) {
+            mbar_init(dispatch_bar(w, 0), 1);
+            mbar_init(dispatch_bar(w, 1), 1);
+        }
         fence_mbar_init();
         tma_prefetch_desc(&map_a);
         tma_prefetch_desc(&map_b);
@@ -110,50 +119,98 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 
     if (is_dispatch) {
         // ------------------------------------------------------------------ dispatch role (all 12 warps)
+        // Each warp owns two 8 KB staging buffers in the (otherwise unused) operand stages.  Its leader streams
+        // the rows through them in chunks with bulk copies: global -> shared (completes on the buffer's
+        // mbarrier), shared -> the destination's slot row (bulk group); the load of chunk c runs while chunk
+        // c-1 is stored.  Rows are published in batches (arrival counter of the row's 128-row block at the
+        // destination): bulk-group wait, one system-scope fence, one red.add per row.
         const int num_send = min(*f.num_send, f.max_send);
         const int warps_total = cd * 2 * (kThreads / 32);
         const int wid = (cluster_id * 2 + (int)rank) * (kThreads / 32) + warp;
-        const int nvec = f.H / 8;
         const int e_local = f.E / f.N;
-        for (int base = wid * 2; base < num_send; base += warps_total * 2) {
-            int blk[2] = {-1, -1};
-            int dst_rank[2] = {0, 0};
+        if (lane == 0) {
+            const uint32_t buf0 = smem_base + (uint32_t)warp * (2 * kDispatchChunk);
+            const uint32_t row_bytes = (uint32_t)f.H * 2u;
+            uint32_t ph0 = 0, ph1 = 0, nchunk = 0;
+            bool ok = true;
+            // chunk whose load is in flight (stored one step later)
+            bool pend = false, pend_last = false;
+            uint64_t pend_dst = 0;
+            uint32_t pend_bytes = 0, pend_b = 0;
+            int pend_blk = 0, pend_d = 0;
+            // rows whose stores are committed but not yet published
+            int pub_blk[kPublishBatch], pub_d[kPublishBatch], npub = 0;
+            auto publish = [&]() {
+                if (npub == 0) return;
+                tma_store_wait<0>();          // the rows' bulk stores have been performed
+                fence_proxy_async_all();
+                fence_acq_rel_sys();          // ... and are ordered, with the table stores, before the counts
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int pos = base + q;
-                if (pos >= num_send) break;
+                for (int i = 0; i < kPublishBatch; ++i)
+                    if (i < npub) red_add_relaxed_sys(reinterpret_cast<int*>(f.ctrl_ptrs[pub_d[i]] + f.off_blk_cnt) + pub_blk[i], 1);
+                npub = 0;
+            };
+            auto store_pending = [&]() -> bool {
+                if (!pend) return true;
+                const uint32_t b = pend_b;
+                if (!mbar_wait(dispatch_bar(warp, b), b ? ph1 : ph0, abort_flag, g.status, 640)) return false;
+                if (b) ph1 ^= 1u; else ph0 ^= 1u;
+                bulk_store_1d(pend_dst, buf0 + b * kDispatchChunk, pend_bytes);
+                tma_store_commit();
+                pend = false;
+                if (pend_last) {
+#pragma unroll
+                    for (int i = 0; i < kPublishBatch; ++i)
+                        if (i == npub) { pub_blk[i] = pend_blk; pub_d[i] = pend_d; }
+                    if (++npub == kPublishBatch) publish();
+                }
+                return true;
+            };
+            for (int pos = wid; ok && pos < num_send; pos += warps_total) {
                 const int entry = f.send_order[pos];
                 const int t = entry / f.K, k = entry - t * f.K;
                 const int e = (int)load_idx(f.topk_idx, f.idx_is64, entry);
                 const int d = e / e_local;
                 const int slot = f.send_slot[entry];
-                if (slot < 0 || slot >= f.slot_cap) continue;   // defensive: never store outside the destination table
+                if (slot < 0 || slot >= f.slot_cap || e < 0 || e >= f.E) continue;   // never store outside the destination table
                 const uint64_t arena = f.arena_ptrs[d];
-                warp_copy_row(reinterpret_cast<int4*>(arena + f.off_slot_x + (uint64_t)slot * f.H * 2),
-                                reinterpret_cast<const int4*>(static_cast<const __nv_bfloat16*>(f.x) + (long)t * f.H), nvec, lane);
-                if (f.with_meta && lane == 0) {
-                    const int row = f.send_row[(long)t * f.N + d];
-                    reinterpret_cast<float*>(arena + f.off_slot_w)[slot] = f.topk_w[entry];
-                    reinterpret_cast<int*>(arena + f.off_slot_tk)[slot] = entry;
-                    reinterpret_cast<int*>(arena + f.off_slot_row)[slot] = row;
-                    bool first = true;                       // first entry of token t that goes to rank d
-                    for (int k2 = 0; k2 < k; ++k2) {
-                        const long long e2 = load_idx(f.topk_idx, f.idx_is64, (long)t * f.K + k2);
-                        if (e2 >= 0 && e2 < f.E && (int)e2 / e_local == d) first = false;
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x) + (size_t)t * row_bytes;
+                const uint64_t dst = arena + f.off_slot_x + (uint64_t)slot * row_bytes;
+                for (uint32_t off = 0; off < row_bytes; off += kDispatchChunk) {
+                    const uint32_t chunk = min((uint32_t)kDispatchChunk, row_bytes - off);
+                    const uint32_t b = nchunk & 1u;
+                    tma_store_wait_read<0>();            // the store that last used this buffer (the newest group) has read it out
+                    mbar_arrive_expect_tx(dispatch_bar(warp, b), chunk);
+                    bulk_load_1d(buf0 + b * kDispatchChunk, src + off, chunk, dispatch_bar(warp, b));
+                    ++nchunk;
+                    // the previous chunk sits in the other buffer
+                    if (!(ok = store_pending())) break;
+                    pend = true;
+                    pend_b = b;
+                    pend_dst = dst + off;
+                    pend_bytes = chunk;
+                    pend_last = off + kDispatchChunk >= row_bytes;
+                    pend_blk = slot >> 7;
+                    pend_d = d;
+                    if (off == 0 && f.with_meta) {
+                        const int row = f.send_row[(long)t * f.N + d];
+                        reinterpret_cast<float*>(arena + f.off_slot_w)[slot] = f.topk_w[entry];
+                        reinterpret_cast<int*>(arena + f.off_slot_tk)[slot] = entry;
+                        reinterpret_cast<int*>(arena + f.off_slot_row)[slot] = row;
+                        bool first = true;                       // first entry of token t that goes to rank d
+                        for (int k2 = 0; k2 < k; ++k2) {
+                            const long long e2 = load_idx(f.topk_idx, f.idx_is64, (long)t * f.K + k2);
+                            if (e2 >= 0 && e2 < f.E && (int)e2 / e_local == d) first = false;
+                        }
+                        if (first) reinterpret_cast<int*>(arena + f.off_row_first)[row] = slot;
                     }
-                    if (first) reinterpret_cast<int*>(arena + f.off_row_first)[row] = slot;
                 }
-                blk[q] = slot >> 7;
-                dst_rank[q] = d;
             }
-            __syncwarp();
-            if (lane == 0) {
-                fence_acq_rel_sys();   // this warp's row and table stores are ordered before the arrival counts
-#pragma unroll
-                for (int q = 0; q < 2; ++q)
-                    if (blk[q] >= 0) red_add_relaxed_sys(reinterpret_cast<int*>(f.ctrl_ptrs[dst_rank[q]] + f.off_blk_cnt) + blk[q], 1);
-            }
+            if (ok) ok = store_pending();
+            if (ok) publish();
+            tma_store_wait<0>();              // nothing of this thread's copies is in flight past this point
         }
+        __syncwarp();
     } else {
         const int cid = cluster_id - cd;
         const int ncc = num_clusters - cd;
@@ -301,6 +358,7 @@ cudaError_t fused_dispatch_gemm(int kind, const void* slot_x, int slot_rows, con
                                 int num_sms, cudaStream_t stream) {
     // kind 0: forward gate_up + SwiGLU (W_gateup [E*2I, H] K-major);  kind 1: backward grad_act + dSwiGLU (W_down [E*H, I] MN-major)
     if (p.H % BK != 0 || p.I % 32 != 0 || slot_rows % BM != 0 || slot_rows <= 0) return cudaErrorInvalidValue;
+    if (reinterpret_cast<uintptr_t>(f.x) % 16 != 0 || f.off_slot_x % 16 != 0) return cudaErrorInvalidValue;   // bulk copies need 16-byte alignment
     CUtensorMap ma, mb;
     cudaError_t e;
     if ((e = make_map(&ma, slot_x, (uint64_t)slot_rows, p.H, BK, BM)) != cudaSuccess) return e;

@@ -458,7 +458,10 @@ class EPEngine:
         h.topk_weights = topk_weights
         st = w.status if self.is_cuda else None
         units = (h.unit_blk, h.num_units) if (self.is_cuda and USE_CTA_PAIRS and h.unit_blk is not None) else None
-        h.fused_dispatch = bool(self.is_cuda and use_fused_dispatch(I, w.size) and use_fused_combine(I, w.size, False)
+        # The fused dispatch kernel waits for rows that OTHER ranks' kernels send, so every rank must be running at the
+        # same time: real ranks (one process per GPU) or a single rank; never the sequential launches of a virtual cluster.
+        concurrent = w.size == 1 or w.virtual_peers is None
+        h.fused_dispatch = bool(self.is_cuda and concurrent and use_fused_dispatch(I, w.size) and use_fused_combine(I, w.size, False)
                                 and use_fused_combine(I, w.size, True))
         if h.fused_dispatch:
             tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms)
