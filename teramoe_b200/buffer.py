@@ -252,7 +252,9 @@ class Buffer(LowLatencyMixin):
         Rows arrive once per (token, rank), ordered by source rank then token.  `recv_topk_idx` holds
         LOCAL expert ids (-1 for experts of other ranks, weights zeroed there), like
         csrc/kernels/intranode.cu:369-378.  With `handle=` (cached mode) only the payload moves and
-        no host synchronisation happens."""
+        no host synchronisation happens.  `num_worst_tokens > 0` gives fixed-shape outputs (padded rows are
+        zero, expert id -1, empty per-expert list); the 32-byte read of the layout sizes still happens, since
+        the arena geometry is sized per call."""
         if isinstance(x, tuple):
             raise NotImplementedError("FP8 (x, scales) payloads are not supported by the bf16 training path")
         x = x.contiguous()
@@ -284,6 +286,16 @@ class Buffer(LowLatencyMixin):
             le = h.mblock_expert.long()[sl // 128] if h.slots > 0 else sl
             recv_idx[rr[valid], kpos[valid]] = le[valid].to(topk_idx.dtype)
             recv_w[rr[valid], kpos[valid]] = h.slot_w[sl[valid]]
+            if num_worst_tokens > 0:
+                # fixed-shape mode (csrc/deep_ep.cpp:377-386): outputs have `num_worst_tokens` rows, rows past the
+                # received count are zero with expert id -1, and no per-expert list is produced
+                if R > num_worst_tokens:
+                    raise RuntimeError(f"received {R} rows, more than num_worst_tokens={num_worst_tokens}")
+                pad = num_worst_tokens - R
+                recv_x = torch.cat([recv_x, recv_x.new_zeros(pad, recv_x.shape[1])])
+                recv_idx = torch.cat([recv_idx, recv_idx.new_full((pad, K), -1)])
+                recv_w = torch.cat([recv_w, recv_w.new_zeros(pad, K)])
+                return recv_x, recv_idx, recv_w, [], h
             counts = h.expert_total_local.tolist()
             counts = [(c + expert_alignment - 1) // expert_alignment * expert_alignment for c in counts]
             return recv_x, recv_idx, recv_w, counts, h

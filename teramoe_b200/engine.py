@@ -378,8 +378,12 @@ class EPEngine:
         received top-k weights back to their source entries.  -> (combined_x [T,H], weights [T,K] | None)."""
         import copy
         R, K, dev = h.rows, h.K, x.device
-        if x.shape[0] != R:
+        if x.shape[0] < R:
             raise ValueError(f"expected {R} rows (one per received token), got {x.shape[0]}")
+        if x.shape[0] > R:      # fixed-shape dispatch outputs (num_worst_tokens): rows past the received count are padding
+            x = x[:R]
+            if recv_topk_weights is not None:
+                recv_topk_weights = recv_topk_weights[:R]
         offs, total, maxima = _arena_geometry(h.maxima, x.shape[1], K)
         if self.is_cuda:
             yield ("grow", total)

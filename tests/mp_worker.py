@@ -64,6 +64,14 @@ def main():
             assert (comb.float() - expect).abs().max().item() <= tol * 4 * max(1.0, expect.abs().max().item())
         valid = idx >= 0
         assert torch.allclose(comb_w[valid], r["w"].to(dev)[valid], atol=1e-6)
+        # fixed-shape mode: padded outputs, the same combine result
+        worst = 2048   # at least the sum of all ranks' token counts in this problem
+        wx, widx, ww, wcounts, whandle, _ = buf.deepep_dispatch(r["x"].to(dev), topk_idx=idx, topk_weights=r["w"].to(dev), num_experts=E,
+                                                                num_worst_tokens=worst)
+        assert wx.shape[0] == worst and widx.shape[0] == worst and wcounts == []
+        assert torch.equal(wx[: recv_x.shape[0]], recv_x) and bool((widx[recv_x.shape[0]:] == -1).all())
+        comb2, _, _ = buf.deepep_combine(wx, whandle)
+        assert torch.equal(comb2, comb)
         buf.destroy()
     elif case == "mismatch":
         # ranks disagree on num_experts: the host-side check must raise on every rank, nothing hangs
