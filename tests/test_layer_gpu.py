@@ -55,7 +55,14 @@ def test_virtual_cluster_fused_and_separate_combine(mode, monkeypatch):
     compare(run_virtual(prob, "cuda"), oracle(prob), 2e-2, 2e-2)
 
 
-def test_ep1_public_api_autograd_and_determinism():
+@pytest.mark.parametrize("fused_dispatch", ["0", "1"])
+def test_ep1_public_api_autograd_and_determinism(fused_dispatch, monkeypatch):
+    """fused_dispatch="1": the one-kernel dispatch + GEMM path (dispatch CTA pairs feed compute CTA pairs through per-block
+    arrival counters), with the combine pushed from the GEMM epilogues."""
+    from teramoe_b200 import engine
+    monkeypatch.setattr(engine, "_FUSED_DISPATCH_MODE", fused_dispatch)
+    if fused_dispatch == "1":
+        monkeypatch.setattr(engine, "_FUSED_MODE", "1")
     # reference accuracy protocol: x ~ 0.1 N(0,1), W ~ 0.02 N(0,1); limits max_abs 1e-2, calc_diff 1e-5, cosine 0.99
     prob = make_problem(1, 512, 1024, 1024, 16, 8, seed=42, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02)
     r = prob["ranks"][0]
