@@ -138,7 +138,8 @@ void zero_pad_rows(torch::Tensor seg_offsets, torch::Tensor expert_total_local, 
 //   offs   : [slot_x, slot_w, slot_tk, slot_row, row_first, blk_cnt(control arena)]
 void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout,
                          std::vector<torch::Tensor> send_t, std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, int64_t E,
-                         int64_t N, bool with_meta, int64_t num_dispatch_clusters, c10::optional<torch::Tensor> status, int64_t num_sms) {
+                         int64_t N, bool with_meta, int64_t num_dispatch_clusters, double dispatch_tile_share, c10::optional<torch::Tensor> status,
+                         int64_t num_sms) {
     TORCH_CHECK(gemm_t.size() == (kind == 0 ? 5u : 7u) && layout.size() == 4 && send_t.size() == (with_meta ? 7u : 6u) &&
                 sym_t.size() == 6 && offs.size() == 6, "fused_dispatch_gemm: wrong argument lists");
     const torch::Tensor& slot_x = gemm_t[0];
@@ -166,6 +167,8 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
     const TopK tk = topk(send_t[1]);
     tmoe::FusedArgs f{};
     f.num_dispatch_clusters = (int)num_dispatch_clusters;
+    TORCH_CHECK(dispatch_tile_share >= 0.0 && dispatch_tile_share < 1.0, "dispatch_tile_share must be in [0, 1)");
+    f.dispatch_tile_share = (float)dispatch_tile_share;
     f.x = bf16(send_t[0], "x");
     f.topk_idx = tk.ptr;
     f.idx_is64 = tk.is64;

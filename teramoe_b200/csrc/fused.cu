@@ -44,9 +44,8 @@ struct TileF {
     int blk0, two, n_blk, group;
 };
 
-__device__ __forceinline__ bool get_tile_f(const GemmArgs& g, const int* unit_order, int t, int num_units, TileF& tile) {
-    const int total = num_units * g.num_n_blocks;
-    if (t >= total) return false;
+__device__ __forceinline__ bool get_tile_f(const GemmArgs& g, const int* unit_order, int t, int t_end, int num_units, TileF& tile) {
+    if (t >= t_end) return false;
     const int per_super = kSuperUF * g.num_n_blocks;
     const int super = t / per_super;
     const int r = t - super * per_super;
@@ -211,12 +210,21 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             tma_store_wait<0>();              // nothing of this thread's copies is in flight past this point
         }
         __syncwarp();
-    } else {
-        const int cid = cluster_id - cd;
-        const int ncc = num_clusters - cd;
+        cluster_sync_all();                   // both CTAs of the pair are done with the staging buffers: they become operand stages
+    }
+
+    // ---------------------------------------------------------------------- compute role
+    // Tiles [0, total - tail) belong to the compute pairs, the last `tail` tiles (the latest arrival groups) to
+    // the dispatch pairs, which take them up once their rows are out.
+    {
         int num_units = g.max_units;
         if (g.num_units_dev != nullptr) num_units = min(*g.num_units_dev, g.max_units);
         const int nk = g.k_total / BK;
+        const int total_tiles = num_units * g.num_n_blocks;
+        const int tail = (cd > 0) ? min(total_tiles, (int)((float)total_tiles * f.dispatch_tile_share)) : 0;
+        const int t_first = is_dispatch ? (total_tiles - tail + cluster_id) : (cluster_id - cd);
+        const int t_end = is_dispatch ? total_tiles : (total_tiles - tail);
+        const int t_stride = is_dispatch ? cd : (num_clusters - cd);
 
         if (warp == 0) {
             // -------------------------------------------------------------- TMA producer
@@ -225,7 +233,7 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
                 uint32_t phase = 0;
                 bool ok = true;
                 TileF tile;
-                for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc) {
+                for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride) {
                     const bool live = (rank == 0) || tile.two;
                     const int my_blk = tile.blk0 + (int)rank;
                     if (live) {
@@ -266,7 +274,7 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             bool ok = true;
             TileF tile;
             int iter = 0;
-            for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc, ++iter) {
+            for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride, ++iter) {
                 const int as = iter & 1;
                 const uint32_t aphase = (iter >> 1) & 1;
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, 620)) { ok = false; break; }
@@ -300,7 +308,7 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             bool ok = true;
             TileF tile;
             int iter = 0;
-            for (int t = cid; ok && get_tile_f(g, f.unit_order, t, num_units, tile); t += ncc, ++iter) {
+            for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride, ++iter) {
                 const int as = iter & 1;
                 const uint32_t aphase = (iter >> 1) & 1;
                 if (!mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, 630)) { ok = false; break; }

@@ -10,7 +10,9 @@ namespace tmoe {
 // What the dispatch pairs need.  Offsets are byte offsets inside every rank's symmetric data arena
 // (arena_ptrs) or control arena (ctrl_ptrs); they are the same on all ranks.
 struct FusedArgs {
-    int num_dispatch_clusters;     // CTA pairs that dispatch; the remaining pairs compute
+    int num_dispatch_clusters;     // CTA pairs that dispatch first; the remaining pairs compute from the start
+    float dispatch_tile_share;     // fraction of all tiles (taken from the end of the arrival order) that the dispatch
+                                   // pairs compute once their rows are out
     const void* x;                 // [T, H] bf16 rows to send (x in forward, grad_out in backward)
     const void* topk_idx;          // [T, K]
     int idx_is64;

@@ -71,7 +71,12 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 # push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
 # rows that arrive.  Used when the CTA-pair kernels are on and the GEMM outlasts the transfer.
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "0")
-FUSED_DISPATCH_CLUSTERS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "6"))
+# CTA pairs given to the dispatch role: "n" or "forward,backward" (the backward GEMM is half as long for the same bytes)
+_pairs = [int(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "8,8").split(",")]
+FUSED_DISPATCH_CLUSTERS = (_pairs[0], _pairs[-1])
+# Share of the GEMM tiles (the latest arrivals) that the dispatch pairs compute after their rows are out: "s" or "forward,backward"
+_share = [float(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_SHARE", "0.0,0.0").split(",")]
+FUSED_DISPATCH_SHARE = (_share[0], _share[-1])
 FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
 
 
@@ -550,7 +555,7 @@ class EPEngine:
                  h.seg_offsets, h.expert_total_local]
         offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset]
         ext.fused_dispatch_gemm(kind, gemm_t, [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units], send_t, sym_t, offsets, E, N,
-                                kind == 0, FUSED_DISPATCH_CLUSTERS, w.status, num_sms)
+                                kind == 0, FUSED_DISPATCH_CLUSTERS[kind], FUSED_DISPATCH_SHARE[kind], w.status, num_sms)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         return tabs, offs, out0, out1, parts
