@@ -134,14 +134,13 @@ void zero_pad_rows(torch::Tensor seg_offsets, torch::Tensor expert_total_local, 
 //   gemm_t : [slot_x view, weights, row_w, out0, out1] (+ [preact, droute_part] for kind 1)
 //   layout : [mblock_expert, num_mblocks, unit_blk, num_units]
 //   send_t : [x, topk_idx, send_order, num_send, send_slot, send_row] (+ [topk_w] when with_meta)
-//   sym_t  : [arena_ptrs, ctrl_ptrs, blk_cnt view, unit_order, seg_offsets, expert_total_local]
+//   sym_t  : [arena_ptrs, ctrl_ptrs, blk_cnt view, unit_order, seg_offsets, expert_total_local, tile_counter (int, zero)]
 //   offs   : [slot_x, slot_w, slot_tk, slot_row, row_first, blk_cnt(control arena)]
 void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout,
                          std::vector<torch::Tensor> send_t, std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, int64_t E,
-                         int64_t N, bool with_meta, int64_t num_dispatch_clusters, double dispatch_tile_share, c10::optional<torch::Tensor> status,
-                         int64_t num_sms) {
+                         int64_t N, bool with_meta, int64_t num_dispatch_clusters, c10::optional<torch::Tensor> status, int64_t num_sms) {
     TORCH_CHECK(gemm_t.size() == (kind == 0 ? 5u : 7u) && layout.size() == 4 && send_t.size() == (with_meta ? 7u : 6u) &&
-                sym_t.size() == 6 && offs.size() == 6, "fused_dispatch_gemm: wrong argument lists");
+                sym_t.size() == 7 && offs.size() == 6, "fused_dispatch_gemm: wrong argument lists");
     const torch::Tensor& slot_x = gemm_t[0];
     const torch::Tensor& w = gemm_t[1];
     const int S = (int)slot_x.size(0), H = (int)slot_x.size(1);
@@ -167,8 +166,6 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
     const TopK tk = topk(send_t[1]);
     tmoe::FusedArgs f{};
     f.num_dispatch_clusters = (int)num_dispatch_clusters;
-    TORCH_CHECK(dispatch_tile_share >= 0.0 && dispatch_tile_share < 1.0, "dispatch_tile_share must be in [0, 1)");
-    f.dispatch_tile_share = (float)dispatch_tile_share;
     f.x = bf16(send_t[0], "x");
     f.topk_idx = tk.ptr;
     f.idx_is64 = tk.is64;
@@ -187,6 +184,8 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
     f.unit_order = i32(sym_t[3], "unit_order");
     f.seg_offsets = i32(sym_t[4], "seg_offsets");
     f.expert_total_local = i32(sym_t[5], "expert_total_local");
+    check_i32(sym_t[6], "tile_counter");
+    f.tile_counter = sym_t[6].data_ptr<int>();
     f.off_slot_x = offs[0]; f.off_slot_w = offs[1]; f.off_slot_tk = offs[2]; f.off_slot_row = offs[3]; f.off_row_first = offs[4];
     f.off_blk_cnt = offs[5];
     TORCH_CHECK(send_t[0].size(1) == H && S % 128 == 0 && sym_t[2].numel() >= S / 128, "fused_dispatch_gemm: shape mismatch");

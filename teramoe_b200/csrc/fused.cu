@@ -8,19 +8,22 @@
 //                    shared memory, one row in flight per warp) and then publish it: bulk-group wait,
 //                    fence.acq_rel.sys + red.add on the destination's per-block arrival counter.
 //                    In forward they also store the slot tables (route weight, entry id, row).
-//   compute pairs    the CTA-pair GEMM of gemm2.cu over the units sorted by arrival group; before the
-//                    first load of a tile the producer thread waits (bounded, ld.acquire.sys) until the
-//                    arrival counter of its 128-row block has reached the block's row count, then
-//                    fence.proxy.async, then TMA.  Weights never wait.
+//                    When its rows are out, a dispatch pair joins the compute pairs.
+//   compute pairs    the CTA-pair GEMM of gemm2.cu over the tiles in arrival order (arrival_order in routing.cu).
+//                    Tiles are claimed from one counter per launch (atomicAdd by the first CTA's producer thread,
+//                    one tile ahead) and handed to the other roles of the pair through a 4-entry ring in each
+//                    CTA's shared memory.  Before the first load of a tile the producer thread waits (bounded,
+//                    ld.acquire.sys) until the arrival counter of its 128-row block has reached the block's row
+//                    count, then fence.proxy.async, then TMA.  Weights never wait.
 //
 // Forward:  GU = Xslots . Wgu^T with the SwiGLU x route epilogue (pre-activation side store).
 // Backward: gA = dYslots . Wd with the dSwiGLU epilogue (dGU, act x route, route-gradient partials).
 //
 // Reference counterpart: the dispatch + compute roles of teramoe_fused_forward_kernel /
 // teramoe_fused_backward_kernel (csrc/teramoe/teramoe_orchestrator.cu:524-1369, :1626-1907, :2978-3042,
-// :4495-4848).  Differences: rows go to their final slot (no ring, no publisher warps, no scheduler SM:
-// the tile order is the static arrival order computed by arrival_order in routing.cu), readiness is
-// one counter per 128-row block, and every wait is bounded.
+// :4495-4848).  Differences: rows go to their final slot (no receive ring, no publisher warps), there is no
+// scheduler SM (tiles are claimed from a counter in the arrival order computed by arrival_order in routing.cu),
+// readiness is one counter per 128-row block, dispatch SMs are reused for compute, and every wait is bounded.
 #include "fused.h"
 
 #include "gemm_common.cuh"
@@ -38,6 +41,10 @@ constexpr int kSmemBytesF = kStagesF * kStageBytesF + 1024 + 512;
 constexpr int kSuperUF = 8;
 constexpr int kDispatchChunk = 8192;                            // two per dispatch warp; 12 warps fill the six operand stages
 constexpr int kPublishBatch = 4;                                // rows published per system-scope fence
+constexpr int kSchedDepth = 4;                                  // entries of the tile ring (the producer runs < 4 tiles ahead of the epilogue)
+constexpr uint32_t kSchedFullOffset = 336, kSchedEmptyOffset = 368, kRingOffset = 400;   // bytes after the pipeline barriers
+// arrivals that release a ring entry: UMMA issuer + 8 epilogue warps of the first CTA, producer + 8 epilogue warps of the second
+constexpr uint32_t kSchedConsumers = 2 * kEpiWarps + 2;
 static_assert((kThreads / 32) * 2 * kDispatchChunk <= kStagesF * kStageBytesF, "dispatch staging exceeds the operand stages");
 
 struct TileF {
@@ -83,6 +90,9 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     volatile uint32_t* abort_flag = tmem_slot + 1;
     auto dispatch_bar = [&](int w, uint32_t b) { return bar_base + 144u + 8u * (2u * w + b); };   // two per dispatch warp, after the flags
 
+    auto sched_full = [&](int e) { return bar_base + kSchedFullOffset + 8u * e; };
+    auto sched_empty = [&](int e) { return bar_base + kSchedEmptyOffset + 8u * e; };
+
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -105,6 +115,10 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         for (int w = 0; w < kThreads / 32; ++w) {
             mbar_init(dispatch_bar(w, 0), 1);
             mbar_init(dispatch_bar(w, 1), 1);
+        }
+        for (int e = 0; e < kSchedDepth; ++e) {
+            mbar_init(sched_full(e), 1);
+            mbar_init(sched_empty(e), kSchedConsumers);
         }
         fence_mbar_init();
         tma_prefetch_desc(&map_a);
@@ -214,26 +228,57 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
     }
 
     // ---------------------------------------------------------------------- compute role
-    // Tiles [0, total - tail) belong to the compute pairs, the last `tail` tiles (the latest arrival groups) to
-    // the dispatch pairs, which take them up once their rows are out.
+    // Tiles are claimed in arrival order from one counter per launch (atomicAdd by the first CTA's producer thread,
+    // one tile ahead) and handed to the other roles of the pair through a small ring in each CTA's shared memory,
+    // so dispatch pairs simply join once their rows are out and uneven tiles balance themselves.
     {
         int num_units = g.max_units;
         if (g.num_units_dev != nullptr) num_units = min(*g.num_units_dev, g.max_units);
         const int nk = g.k_total / BK;
         const int total_tiles = num_units * g.num_n_blocks;
-        const int tail = (cd > 0) ? min(total_tiles, (int)((float)total_tiles * f.dispatch_tile_share)) : 0;
-        const int t_first = is_dispatch ? (total_tiles - tail + cluster_id) : (cluster_id - cd);
-        const int t_end = is_dispatch ? total_tiles : (total_tiles - tail);
-        const int t_stride = is_dispatch ? cd : (num_clusters - cd);
+        const uint32_t ring_addr = bar_base + kRingOffset;
+        volatile int* ring = reinterpret_cast<volatile int*>(smem_gen + kStagesF * kStageBytesF + kRingOffset);
+        // consumer side of the ring: wait for entry `ss`, copy it, release the entry (to the first CTA's scheduler)
+        auto next_tile = [&](int& ss, uint32_t& sph, int site, int& t) -> bool {
+            if (!mbar_wait_cluster_acquire(sched_full(ss), sph, abort_flag, g.status, site)) return false;
+            t = ring[ss];
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(sched_empty(ss));
+                else mbar_arrive_cluster(mapa_shared(sched_empty(ss), 0));
+            }
+            if (++ss == kSchedDepth) { ss = 0; sph ^= 1u; }
+            return true;
+        };
 
         if (warp == 0) {
-            // -------------------------------------------------------------- TMA producer
+            // -------------------------------------------------------------- tile scheduler (first CTA) + TMA producer
             if (elect_one()) {
                 int stage = 0;
                 uint32_t phase = 0;
                 bool ok = true;
                 TileF tile;
-                for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride) {
+                int ss = 0;
+                uint32_t sph = 0;
+                int t_next = (rank == 0) ? atomicAdd(f.tile_counter, 1) : 0;
+                while (ok) {
+                    int t;
+                    if (rank == 0) {
+                        t = (t_next < total_tiles) ? t_next : -1;
+                        if (t >= 0) t_next = atomicAdd(f.tile_counter, 1);   // its latency hides under this tile's loads
+                        if (!mbar_wait(sched_empty(ss), sph ^ 1u, abort_flag, g.status, 650)) { ok = false; break; }
+                        ring[ss] = t;
+                        st_shared_cluster_u32(mapa_shared(ring_addr + 4u * ss, 1), (uint32_t)t);
+                        mbar_arrive(sched_full(ss));
+                        mbar_arrive_cluster_release(mapa_shared(sched_full(ss), 1));
+                    } else {
+                        if (!mbar_wait_cluster_acquire(sched_full(ss), sph, abort_flag, g.status, 651)) { ok = false; break; }
+                        t = ring[ss];
+                        mbar_arrive_cluster(mapa_shared(sched_empty(ss), 0));
+                    }
+                    if (++ss == kSchedDepth) { ss = 0; sph ^= 1u; }
+                    if (t < 0) break;
+                    get_tile_f(g, f.unit_order, t, total_tiles, num_units, tile);
                     const bool live = (rank == 0) || tile.two;
                     const int my_blk = tile.blk0 + (int)rank;
                     if (live) {
@@ -272,9 +317,11 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            TileF tile;
-            int iter = 0;
-            for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride, ++iter) {
+            int ss = 0;
+            uint32_t sph = 0;
+            for (int iter = 0; ok; ++iter) {
+                int t;
+                if (!next_tile(ss, sph, 652, t) || t < 0) break;
                 const int as = iter & 1;
                 const uint32_t aphase = (iter >> 1) & 1;
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1u, abort_flag, g.status, 620)) { ok = false; break; }
@@ -307,8 +354,12 @@ fused_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             const int r = q * 32 + lane;
             bool ok = true;
             TileF tile;
-            int iter = 0;
-            for (int t = t_first; ok && get_tile_f(g, f.unit_order, t, t_end, num_units, tile); t += t_stride, ++iter) {
+            int ss = 0;
+            uint32_t sph = 0;
+            for (int iter = 0; ok; ++iter) {
+                int t;
+                if (!next_tile(ss, sph, 653, t) || t < 0) break;
+                get_tile_f(g, f.unit_order, t, total_tiles, num_units, tile);
                 const int as = iter & 1;
                 const uint32_t aphase = (iter >> 1) & 1;
                 if (!mbar_wait(tfull_bar(as), aphase, abort_flag, g.status, 630)) { ok = false; break; }

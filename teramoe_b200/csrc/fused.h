@@ -10,9 +10,8 @@ namespace tmoe {
 // What the dispatch pairs need.  Offsets are byte offsets inside every rank's symmetric data arena
 // (arena_ptrs) or control arena (ctrl_ptrs); they are the same on all ranks.
 struct FusedArgs {
-    int num_dispatch_clusters;     // CTA pairs that dispatch first; the remaining pairs compute from the start
-    float dispatch_tile_share;     // fraction of all tiles (taken from the end of the arrival order) that the dispatch
-                                   // pairs compute once their rows are out
+    int num_dispatch_clusters;     // CTA pairs that dispatch first and then join the others on the GEMM tiles
+    int* tile_counter;             // device int, zero before the kernel: next GEMM tile to claim
     const void* x;                 // [T, H] bf16 rows to send (x in forward, grad_out in backward)
     const void* topk_idx;          // [T, K]
     int idx_is64;

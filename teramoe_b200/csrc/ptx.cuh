@@ -237,6 +237,47 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same arrive with a cluster-scope release, for the rare arrive that DOES publish data (a word stored into
+// the other CTA's shared memory just before it); pairs with mbar_wait_cluster_acquire.
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (same contract as mbar_wait).
+__device__ __forceinline__ bool mbar_wait_cluster_acquire(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, int* status,
+                                                          int site) {
+#pragma unroll 1
+    for (int i = 0; i < 2048; ++i)
+        if (mbar_try_wait_cluster_acquire(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait_cluster_acquire(bar, parity)) return true;
+        if (*abort_flag != 0u) return false;
+        if (globaltimer_ns() - t0 > TMOE_WAIT_LIMIT_NS) {
+            *abort_flag = 1u;
+            report_status(status, kStatusMbarTimeout, site, (int)parity);
+            return false;
+        }
+    }
+}
 __device__ __forceinline__ void tmem_alloc_2cta(uint32_t dst_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");

@@ -71,12 +71,9 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 # push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
 # rows that arrive.  Used when the CTA-pair kernels are on and the GEMM outlasts the transfer.
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "0")
-# CTA pairs given to the dispatch role: "n" or "forward,backward" (the backward GEMM is half as long for the same bytes)
+# CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
 _pairs = [int(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "8,8").split(",")]
 FUSED_DISPATCH_CLUSTERS = (_pairs[0], _pairs[-1])
-# Share of the GEMM tiles (the latest arrivals) that the dispatch pairs compute after their rows are out: "s" or "forward,backward"
-_share = [float(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_SHARE", "0.0,0.0").split(",")]
-FUSED_DISPATCH_SHARE = (_share[0], _share[-1])
 FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
 
 
@@ -552,10 +549,10 @@ class EPEngine:
         if kind == 0:
             send_t.append(topk_weights)
         sym_t = [w.ptr_table(w.data, 0, "data"), w.ptr_table(w.control, 0, "control_base"), w.blk_cnt_view(), h.unit_order,
-                 h.seg_offsets, h.expert_total_local]
+                 h.seg_offsets, h.expert_total_local, torch.zeros(1, dtype=torch.int32, device=dev)]
         offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset]
         ext.fused_dispatch_gemm(kind, gemm_t, [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units], send_t, sym_t, offsets, E, N,
-                                kind == 0, FUSED_DISPATCH_CLUSTERS[kind], FUSED_DISPATCH_SHARE[kind], w.status, num_sms)
+                                kind == 0, FUSED_DISPATCH_CLUSTERS[kind], w.status, num_sms)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         return tabs, offs, out0, out1, parts
