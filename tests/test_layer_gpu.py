@@ -33,6 +33,16 @@ def test_routing_kernels_match_spec(N, T, E, K, idx_dtype):
             seg, me = L.recv_tables(r, E, N, gl)
             assert torch.equal(h.seg_offsets.cpu(), seg)
             assert (h.rows, h.slots, h.land_rows) == (int(gl.rows[r]), int(gl.slots_padded[r]), int(gl.land_rows[r]))
+            # sending order of the fused dispatch: every routed entry once, destinations in rotation starting with
+            # this rank, and increasing slots inside a destination
+            idx = prob["ranks"][r]["idx"].cpu().long().reshape(-1)
+            valid = ((idx >= 0) & (idx < E)).nonzero(as_tuple=True)[0]
+            ns = int(h.num_send.cpu()[0])
+            order = h.send_order.cpu().long()[:ns]
+            assert ns == valid.numel() and torch.equal(order.sort().values, valid)
+            phase = (idx[order] // (E // N) - r) % N
+            key = phase * (1 << 32) + sl.send_slot.reshape(-1).long()[order]
+            assert bool((key[1:] > key[:-1]).all())
     finally:
         cluster.close()
 
