@@ -69,20 +69,25 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 
 # Dispatch fused into the GEMM that consumes it (csrc/fused.cu): one cooperative kernel, a few CTA pairs
 # push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
-# rows that arrive.  Used when the CTA-pair kernels are on and the GEMM outlasts the transfer.
-_FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "0")
+# rows that arrive; the dispatch pairs join the GEMM when their rows are out.  "auto": with more than one rank,
+# when the GEMM outlasts the transfer (same rule as the fused combine, which it requires) and the slot-space
+# operand table, which then lives in the symmetric arena, stays under FUSED_DISPATCH_MAX_BYTES.
+# Measured (H=7168, I=2048, top-8, 8192 tokens/rank, step ms fused / separate on the same box):
+# EP=1 15.4-15.9 / 15.7, EP=2 17.0 / 17.4, EP=8 19.0 / 19.1.
+_FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "auto")
+FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "4e9")))
 # CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
-_pairs = [int(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "8,8").split(",")]
+_pairs = [int(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "16,16").split(",")]
 FUSED_DISPATCH_CLUSTERS = (_pairs[0], _pairs[-1])
 FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
 
 
-def use_fused_dispatch(I: int, num_ranks: int) -> bool:
+def use_fused_dispatch(I: int, num_ranks: int, table_bytes: int = 0) -> bool:
     if not USE_CTA_PAIRS or USE_TMA_GATHER:
         return False
     if _FUSED_DISPATCH_MODE in ("0", "1"):
         return _FUSED_DISPATCH_MODE == "1"
-    return I >= 1536
+    return num_ranks > 1 and I >= 1536 and table_bytes <= FUSED_DISPATCH_MAX_BYTES
 
 
 @dataclass
@@ -467,7 +472,8 @@ class EPEngine:
         # The fused dispatch kernel waits for rows that OTHER ranks' kernels send, so every rank must be running at the
         # same time: real ranks (one process per GPU) or a single rank; never the sequential launches of a virtual cluster.
         concurrent = w.size == 1 or w.virtual_peers is None
-        h.fused_dispatch = bool(self.is_cuda and concurrent and use_fused_dispatch(I, w.size) and use_fused_combine(I, w.size, False)
+        h.fused_dispatch = bool(self.is_cuda and concurrent and use_fused_dispatch(I, w.size, h.maxima[1] * H * x.element_size())
+                                and use_fused_combine(I, w.size, False)
                                 and use_fused_combine(I, w.size, True))
         if h.fused_dispatch:
             tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms)

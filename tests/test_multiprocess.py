@@ -50,3 +50,12 @@ def test_nccl_layer_all_gpus():
     world = torch.cuda.device_count()
     world = 8 if world >= 8 else 4 if world >= 4 else 2
     _launch("nccl", "layer", world, timeout=600)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_layer_fused_dispatch_and_combine():
+    """The one-kernel dispatch + GEMM path and the combine pushed from the GEMM epilogues, forced on for the small test shapes."""
+    world = torch.cuda.device_count()
+    world = 8 if world >= 8 else 4 if world >= 4 else 2
+    _launch("nccl", "layer", world, timeout=600, extra_env={"TERAMOE_FUSED_COMBINE": "1", "TERAMOE_FUSED_DISPATCH": "1"})
