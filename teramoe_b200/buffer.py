@@ -25,6 +25,22 @@ from .utils.events import EventHandle, EventOverlap
 from .utils.nvlink import check_nvlink_connections
 
 
+def _rows_as_bf16(t: torch.Tensor) -> torch.Tensor:
+    """[T, C] of any dtype -> the same bytes as bf16 rows, zero-padded to a multiple of 16 bytes per row."""
+    t = t.contiguous()
+    raw = t.view(torch.uint8).reshape(t.shape[0], t.shape[1] * t.element_size())
+    pad = (-raw.shape[1]) % 16
+    if pad:
+        raw = torch.cat([raw, raw.new_zeros(raw.shape[0], pad)], dim=1)
+    return raw.contiguous().view(torch.bfloat16)
+
+
+def _rows_from_bf16(rows: torch.Tensor, dtype: torch.dtype, cols: int) -> torch.Tensor:
+    raw = rows.contiguous().view(torch.uint8).reshape(rows.shape[0], rows.shape[1] * rows.element_size())
+    nbytes = cols * torch.empty((), dtype=dtype).element_size()
+    return raw[:, :nbytes].contiguous().view(dtype)
+
+
 class _TeraMoEFunction(torch.autograd.Function):
     """Autograd wrapper of the layer: gradients for x, topk_weights, W_gateup and W_down."""
 
@@ -256,7 +272,18 @@ class Buffer(LowLatencyMixin):
         zero, expert id -1, empty per-expert list); the 32-byte read of the layout sizes still happens, since
         the arena geometry is sized per call."""
         if isinstance(x, tuple):
-            raise NotImplementedError("FP8 (x, scales) payloads are not supported by the bf16 training path")
+            # FP8 payload (x_e4m3 [T,H], scales [T,H/128] fp32), teramoe/buffer.py:344-346: both parts travel as raw
+            # bytes through the same kernels (the second with the cached handle) and come back as a tuple
+            xq, xs = x
+            res = self.deepep_dispatch(_rows_as_bf16(xq), handle, num_tokens_per_rank, num_tokens_per_rdma_rank, is_token_in_rank,
+                                       num_tokens_per_expert, topk_idx, topk_weights, expert_alignment, num_worst_tokens, config,
+                                       previous_event, False, allocate_on_comm_stream, num_experts)
+            recv_q = _rows_from_bf16(res[0], xq.dtype, xq.shape[1])
+            recv_s, *_rest = self.deepep_dispatch(_rows_as_bf16(xs), res[4])
+            recv_s = _rows_from_bf16(recv_s, xs.dtype, xs.shape[1])
+            if recv_q.shape[0] > recv_s.shape[0]:      # fixed-shape mode pads the payload rows only
+                recv_s = torch.cat([recv_s, recv_s.new_zeros(recv_q.shape[0] - recv_s.shape[0], recv_s.shape[1])])
+            return ((recv_q, recv_s), *res[1:])
         x = x.contiguous()
 
         def run():

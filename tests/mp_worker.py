@@ -72,6 +72,16 @@ def main():
         assert torch.equal(wx[: recv_x.shape[0]], recv_x) and bool((widx[recv_x.shape[0]:] == -1).all())
         comb2, _, _ = buf.deepep_combine(wx, whandle)
         assert torch.equal(comb2, comb)
+        # FP8 payload: (e4m3 rows, per-128-channel scales) travel as raw bytes and arrive in the order of recv_x
+        from teramoe_b200.low_latency import fp8_dequantize, fp8_quantize
+        x8 = torch.randn(idx.shape[0], 256, generator=torch.Generator().manual_seed(100 + rank)).to(dev).to(r["x"].dtype)
+        q, sc = fp8_quantize(x8)
+        (rq, rsc), _, _, _, h8, _ = buf.deepep_dispatch((q, sc), topk_idx=idx, topk_weights=r["w"].to(dev), num_experts=E)
+        want, *_ = buf.deepep_dispatch(x8, handle=h8)
+        assert rq.dtype == q.dtype and rq.shape == want.shape and rsc.shape == (want.shape[0], sc.shape[1])
+        if want.numel():
+            err = (fp8_dequantize(rq, rsc, torch.float32) - want.float()).abs().max().item()
+            assert err <= 0.07 * max(1.0, want.float().abs().max().item()), err
         buf.destroy()
     elif case == "mismatch":
         # ranks disagree on num_experts: the host-side check must raise on every rank, nothing hangs
