@@ -35,3 +35,45 @@ def test_barrier_wait_runs_out_and_reports():
         cluster.worlds[1].status.zero_()
     finally:
         cluster.close()
+
+
+def test_fused_dispatch_gemm_wait_runs_out_and_reports():
+    """The compute pairs of the one-kernel dispatch + GEMM wait for arrival counters.  With a sending list of length
+    zero no counter ever fills: every wait runs out its limit, the kernel frees its tensor memory and returns, the status
+    block names the wait, and the same buffer runs a normal layer afterwards."""
+    import teramoe_b200 as tm
+    from teramoe_b200 import engine
+
+    torch.manual_seed(3)
+    T, H, I, E, K = 256, 256, 256, 4, 2
+    x = (torch.randn(T, H, device="cuda") * 0.1).to(torch.bfloat16)
+    Wg = (torch.randn(E, 2 * I, H, device="cuda") * 0.02).to(torch.bfloat16)
+    Wd = (torch.randn(E, H, I, device="cuda") * 0.02).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(T)])
+    w = torch.rand(T, K, device="cuda")
+    buf = tm.Buffer(None, int(64e6), explicitly_destroy=True)
+    try:
+        eng, world = buf._engine, buf._world
+        h = buf._drive(eng.layout_gen(idx, E))
+        h.topk_weights = w
+        h.num_send = torch.zeros_like(h.num_send)          # the dispatch role sends nothing
+        buf._drive(eng.fused_dispatch_gemm_gen(h, x, w, Wg, 0))
+        torch.cuda.synchronize()
+        st = world.status.tolist()
+        assert st[0] in (1, 2) and 600 <= st[1] < 660, st  # a flag or mbarrier wait of the fused kernel
+        with pytest.raises(RuntimeError, match="wait ran out"):
+            world.check_status()
+        assert world.status.tolist()[0] == 0
+        # the context and the buffer are still usable
+        saved_mode = engine._FUSED_DISPATCH_MODE
+        try:
+            engine._FUSED_DISPATCH_MODE = "1"
+            out = buf.teramoe_forward(x, idx, w, Wg, Wd, E)
+        finally:
+            engine._FUSED_DISPATCH_MODE = saved_mode
+        ref = tm.moe_reference(x.float(), idx, w, Wg.float(), Wd.float())
+        torch.cuda.synchronize()
+        assert world.status.tolist()[0] == 0
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    finally:
+        buf.destroy()
