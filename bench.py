@@ -118,7 +118,7 @@ def main():
         run_layer = lambda x, idx, w: layer(x, idx, w, Wg, Wd, chunked=True)
     else:
         buf = tm.Buffer(group, int(2e9), int(1e9) if world > 8 else 0, explicitly_destroy=True)
-        run_layer = lambda x, idx, w: buf.teramoe_autograd(x, idx, w, Wg, Wd, E, num_dispatch_sms=48, num_combine_sms=48)
+        run_layer = lambda x, idx, w: buf.teramoe_autograd(x, idx, w, Wg, Wd, E, num_dispatch_sms=32, num_combine_sms=32)
 
     x_dev, go_dev, idx_dev, w_dev = x_host.to(dev), go_host.to(dev), idx_host.to(dev), w_host.to(dev)
 

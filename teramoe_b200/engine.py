@@ -77,8 +77,16 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "auto")
 FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "4e9")))
 # CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
-_pairs = [int(v) for v in os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS", "16,16").split(",")]
+# Unset: the layer's `num_dispatch_sms` argument decides (two SMs per pair), like the reference's dispatch-SM knob.
+_pairs_env = os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS")
+_pairs = [int(v) for v in (_pairs_env or "16,16").split(",")]
 FUSED_DISPATCH_CLUSTERS = (_pairs[0], _pairs[-1])
+
+
+def dispatch_pairs(kind: int, num_dispatch_sms: int = 0) -> int:
+    if _pairs_env is None and num_dispatch_sms > 0:
+        return max(2, min(48, num_dispatch_sms // 2))
+    return FUSED_DISPATCH_CLUSTERS[kind]
 FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
 
 
@@ -116,6 +124,7 @@ class LayerHandle:
     num_send: Optional[torch.Tensor] = None      # device scalar: number of entries in send_order
     unit_order: Optional[torch.Tensor] = None    # fused dispatch: units sorted by arrival group
     fused_dispatch: bool = False
+    num_dispatch_sms: int = 0                    # SMs that dispatch first in the fused dispatch + GEMM kernel (0: default)
     unit_blk: Optional[torch.Tensor] = None      # CTA-pair GEMMs: first block of every unit (+ sentinel)
     num_units: Optional[torch.Tensor] = None
     slot_row: Optional[torch.Tensor] = None
@@ -476,7 +485,9 @@ class EPEngine:
                                 and use_fused_combine(I, w.size, False)
                                 and use_fused_combine(I, w.size, True))
         if h.fused_dispatch:
-            tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms)
+            h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
+            tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms,
+                                                                                 num_dispatch_sms=h.num_dispatch_sms)
             self._mark("fwd:dispatch + gate_up GEMM (one kernel)")
             R, S = h.rows, h.slots
             h.slot_row, h.slot_w, h.slot_tk = tabs["slot_row"][:S].clone(), tabs["slot_w"][:S].clone(), tabs["slot_tk"][:S].clone()
@@ -520,7 +531,8 @@ class EPEngine:
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
 
-    def fused_dispatch_gemm_gen(self, h: LayerHandle, rows_in, topk_weights, weights, kind: int, preact=None, num_sms=0):
+    def fused_dispatch_gemm_gen(self, h: LayerHandle, rows_in, topk_weights, weights, kind: int, preact=None, num_sms=0,
+                                num_dispatch_sms=0):
         """Dispatch fused with the GEMM that consumes it (csrc/fused.cu).  kind 0: forward, rows_in = x, weights =
         W_gateup -> (act, preact); kind 1: backward, rows_in = grad_out, weights = W_down -> (act_w, dGU, route partials).
         Also returns the table views and offsets of this call."""
@@ -558,7 +570,7 @@ class EPEngine:
                  h.seg_offsets, h.expert_total_local, torch.zeros(1, dtype=torch.int32, device=dev)]
         offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset]
         ext.fused_dispatch_gemm(kind, gemm_t, [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units], send_t, sym_t, offsets, E, N,
-                                kind == 0, FUSED_DISPATCH_CLUSTERS[kind], w.status, num_sms)
+                                kind == 0, dispatch_pairs(kind, num_dispatch_sms), w.status, num_sms)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         return tabs, offs, out0, out1, parts
@@ -575,7 +587,7 @@ class EPEngine:
         self._mark("bwd:start")
         if h.fused_dispatch:
             tabs, offs, act_w, dgu, parts = yield from self.fused_dispatch_gemm_gen(h, grad_out, None, W_down, 1, preact=saved.preact,
-                                                                                    num_sms=num_sms)
+                                                                                    num_sms=num_sms, num_dispatch_sms=h.num_dispatch_sms)
             self._mark("bwd:dispatch + grad_act GEMM (one kernel)")
             units = (h.unit_blk, h.num_units)
             dyperm = tabs["slot_x"][: h.slots]
