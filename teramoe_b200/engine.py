@@ -472,6 +472,7 @@ class EPEngine:
         I = W_gateup.shape[1] // 2
         if W_gateup.shape[2] != H or tuple(W_down.shape[1:]) != (H, I):
             raise ValueError("weight shapes must be W_gateup [E_local, 2I, H] and W_down [E_local, H, I]")
+        num_sms = num_sms or self._grid_sms(impl)
         self._mark("fwd:start")
         h = yield from self.layout_gen(topk_idx, num_experts)
         self._mark("fwd:routing+layout")
@@ -531,6 +532,14 @@ class EPEngine:
         saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
         return out, saved
 
+    def _grid_sms(self, impl) -> int:
+        """`total_sms` of the layer call limits the grids of the GEMM kernels (0: all SMs of the device)."""
+        total = int((impl or {}).get("total_sms", 0))
+        if not self.is_cuda or total <= 0:
+            return 0
+        have = torch.cuda.get_device_properties(self.world.device).multi_processor_count
+        return 0 if total >= have else max(4, total & ~1)
+
     def fused_dispatch_gemm_gen(self, h: LayerHandle, rows_in, topk_weights, weights, kind: int, preact=None, num_sms=0,
                                 num_dispatch_sms=0):
         """Dispatch fused with the GEMM that consumes it (csrc/fused.cu).  kind 0: forward, rows_in = x, weights =
@@ -584,6 +593,7 @@ class EPEngine:
         h = saved.handle
         El = W_gateup.shape[0]
         st = w.status if self.is_cuda else None
+        num_sms = num_sms or self._grid_sms(impl)
         self._mark("bwd:start")
         if h.fused_dispatch:
             tabs, offs, act_w, dgu, parts = yield from self.fused_dispatch_gemm_gen(h, grad_out, None, W_down, 1, preact=saved.preact,

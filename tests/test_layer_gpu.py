@@ -154,3 +154,24 @@ def test_reference_accuracy_case_ep1():
                             ("dW_gateup", Wgl.grad, Wgr.grad), ("dW_down", Wdl.grad, Wdr.grad)):
         assert_close_bf16(got.float(), want.detach().float(), name)
     buf.destroy()
+
+
+@pytest.mark.parametrize("fused_dispatch", ["0", "1"])
+def test_sm_knobs_limit_the_grids(fused_dispatch, monkeypatch):
+    """total_sms limits the GEMM grids and num_dispatch_sms the pairs that dispatch first; results do not change."""
+    from teramoe_b200 import engine
+    monkeypatch.setattr(engine, "_FUSED_DISPATCH_MODE", fused_dispatch)
+    prob = make_problem(1, 384, 512, 512, 8, 4, seed=11, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02)
+    r = prob["ranks"][0]
+    buf = tm.Buffer(None, int(64e6), explicitly_destroy=True)
+    outs = []
+    for kw in ({}, {"total_sms": 64, "num_dispatch_sms": 8, "num_combine_sms": 8}):
+        x = r["x"].clone().requires_grad_(True)
+        Wg = prob["W_gateup"].clone().requires_grad_(True)
+        out = buf.teramoe_autograd(x, r["idx"], r["w"].clone(), Wg, prob["W_down"].clone(), 8, **kw)
+        out.backward(r["go"])
+        outs.append((out.detach(), x.grad, Wg.grad))
+    torch.cuda.synchronize()
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    buf.destroy()
