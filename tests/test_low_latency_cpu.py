@@ -67,3 +67,21 @@ def test_rank_mask_api():
     assert status.tolist() == [0]
     with pytest.raises(RuntimeError):
         tm.Buffer(None, device="cpu").low_latency_clean_mask_buffer()
+
+
+def test_unfused_dispatch_fp8_tuple_and_fixed_shape():
+    """deepep_dispatch with an (e4m3 rows, scales) payload returns the same bytes in the order of the plain payload;
+    num_worst_tokens pads every output to a fixed number of rows."""
+    x, idx, w = _problem(T=48, H=512, E=8, K=2, seed=3)
+    buf = tm.Buffer(None, device="cpu")
+    q, sc = fp8_quantize(x)
+    (rq, rs), ridx, rw, counts, handle, _ = buf.deepep_dispatch((q, sc), topk_idx=idx, topk_weights=w, num_experts=8)
+    plain, *_ = buf.deepep_dispatch(x, handle=handle)
+    assert rq.dtype == q.dtype and rs.dtype == sc.dtype and sum(counts) == idx.numel()
+    q2, sc2 = fp8_quantize(plain)
+    assert torch.equal(rq.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(rs, sc2)
+    (pq, ps), pidx, pw, pcounts, h2, _ = buf.deepep_dispatch((q, sc), topk_idx=idx, topk_weights=w, num_experts=8, num_worst_tokens=96)
+    assert pq.shape == (96, 512) and ps.shape == (96, 4) and pidx.shape == (96, 2) and pcounts == []
+    assert bool((pidx[rq.shape[0]:] == -1).all()) and torch.equal(pq[: rq.shape[0]].view(torch.uint8), rq.view(torch.uint8))
+    comb, _, _ = buf.deepep_combine(fp8_dequantize(pq, ps, torch.float32), h2)
+    assert (comb - x).abs().max().item() <= 0.07 * x.abs().max().item()      # one rank: every token comes back once
