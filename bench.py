@@ -277,6 +277,7 @@ def main():
             "config": {"model": f"moe_layer[{args.config}] H={H} I={I} experts/rank={El} experts={E} top{K}", "global_batch": T * world,
                        "seq_len": T, "tokens_per_rank": T, "parallelism": f"ep{world}", "peak_to_mean": p2m,
                        "l2": "inputs larger than L2 (expert weights %.1f GB per rank are re-read every step)" % (El * 3 * H * I * 2 / 1e9)},
+            "paths": (dict(getattr(buf._engine, "last_paths", {})) if args.impl == "teramoe" else None),
             "tokens_per_s": round(T * world / (ms_max * 1e-3), 1),
             "tflops_per_gpu": round(flops / (ms_max * 1e-3) / 1e12, 1),
             "activation_mb": round(act_max, 2),

@@ -485,6 +485,10 @@ class EPEngine:
         h.fused_dispatch = bool(self.is_cuda and concurrent and use_fused_dispatch(I, w.size, h.maxima[1] * H * x.element_size())
                                 and use_fused_combine(I, w.size, False)
                                 and use_fused_combine(I, w.size, True))
+        # which fused kernels this call uses (read by the benchmark and by Buffer.state())
+        self.last_paths = {"fused_dispatch_gemm": h.fused_dispatch, "cta_pairs": bool(units is not None),
+                           "fused_combine_fwd": bool(self.is_cuda and use_fused_combine(I, w.size, False)),
+                           "fused_combine_bwd": bool(self.is_cuda and use_fused_combine(I, w.size, True))}
         if h.fused_dispatch:
             h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
             tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms,
