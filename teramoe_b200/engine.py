@@ -69,11 +69,11 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 
 # Dispatch fused into the GEMM that consumes it (csrc/fused.cu): one cooperative kernel, a few CTA pairs
 # push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
-# rows that arrive; the dispatch pairs join the GEMM when their rows are out.  "auto": with more than one rank,
-# when the GEMM outlasts the transfer (same rule as the fused combine, which it requires) and the slot-space
-# operand table, which then lives in the symmetric arena, stays under FUSED_DISPATCH_MAX_BYTES.
+# rows that arrive; the dispatch pairs join the GEMM when their rows are out.  "auto": when the GEMM outlasts
+# the transfer (same rule as the fused combine, which it requires) and the slot-space operand table, which
+# then lives in the symmetric arena, stays under FUSED_DISPATCH_MAX_BYTES.
 # Measured (H=7168, I=2048, top-8, 8192 tokens/rank, step ms fused / separate on the same box):
-# EP=1 15.4-15.9 / 15.7, EP=2 17.0 / 17.4, EP=8 19.0 / 19.1.
+# EP=1 16.0 / 16.5 and 16.3 / 17.0 (two boxes' clocks), EP=2 17.0 / 17.4, EP=8 19.0 / 19.1.
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "auto")
 FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "4e9")))
 # CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
@@ -95,7 +95,7 @@ def use_fused_dispatch(I: int, num_ranks: int, table_bytes: int = 0) -> bool:
         return False
     if _FUSED_DISPATCH_MODE in ("0", "1"):
         return _FUSED_DISPATCH_MODE == "1"
-    return num_ranks > 1 and I >= 1536 and table_bytes <= FUSED_DISPATCH_MAX_BYTES
+    return I >= 1536 and table_bytes <= FUSED_DISPATCH_MAX_BYTES
 
 
 @dataclass
