@@ -47,6 +47,7 @@ def parse():
     p.add_argument("--config", default="dsv3", choices=sorted(CONFIGS))
     p.add_argument("--tokens", type=int, default=0, help="override tokens per rank")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--baseline-loop", action="store_true", help="--impl nccl: per-expert GEMM loop instead of the library grouped GEMM")
     p.add_argument("--trace", action="store_true", help="print per-phase device times (rank 0, stderr) after the timed region")
     return p.parse_args()
 
@@ -112,7 +113,8 @@ def main():
 
     if args.impl == "nccl":
         from teramoe_b200.parallel.nccl_baseline import NcclMoEBaseline
-        layer = NcclMoEBaseline(group, E)
+        # library grouped GEMMs (torch.nn.functional.grouped_mm) unless --baseline-loop asks for one cuBLAS GEMM per expert
+        layer = NcclMoEBaseline(group, E, grouped=not args.baseline_loop)
         # the baseline keeps its gate/up weights in the layout a library SwiGLU prefers (gate rows, then up rows)
         Wg = NcclMoEBaseline.to_chunked(Wg.detach()).requires_grad_(True)
         run_layer = lambda x, idx, w: layer(x, idx, w, Wg, Wd, chunked=True)

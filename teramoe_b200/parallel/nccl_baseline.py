@@ -51,8 +51,9 @@ class _PermuteRows(torch.autograd.Function):
 
 
 class NcclMoEBaseline:
-    def __init__(self, group: Optional[dist.ProcessGroup], num_experts: int):
+    def __init__(self, group: Optional[dist.ProcessGroup], num_experts: int, grouped: bool = False):
         self.group = group
+        self.grouped = grouped and hasattr(torch.nn.functional, "grouped_mm")
         self.N = dist.get_world_size(group) if group is not None else 1
         self.E = num_experts
         self.El = num_experts // self.N
@@ -108,6 +109,14 @@ class NcclMoEBaseline:
         inv[sort_idx] = torch.arange(S, device=x.device)
         xe = _PermuteRows.apply(recv, sort_idx, inv)
         per_expert = recv_h.sum(0).tolist()
+        if self.grouped and chunked and S > 0:
+            # one library grouped GEMM per stage (torch.nn.functional.grouped_mm) instead of a loop over experts
+            offs = torch.cumsum(recv_cnt.sum(0), 0).to(torch.int32)
+            gu = torch.nn.functional.grouped_mm(xe, W_gateup.transpose(-2, -1), offs=offs)
+            g, u = gu.chunk(2, dim=1)
+            ye = torch.nn.functional.grouped_mm(torch.nn.functional.silu(g) * u, W_down.transpose(-2, -1), offs=offs)
+            return self._finish(ye, inv, sort_idx, in_splits, out_splits, all_valid, ent, inv_ent if all_valid else None, tok,
+                                topk_weights, T, K, H, x)
         outs = []
         o = 0
         for le in range(El):
@@ -124,6 +133,10 @@ class NcclMoEBaseline:
             outs.append(act @ W_down[le].t())
             o += c
         ye = torch.cat(outs) if outs else xe.new_zeros(0, H)
+        return self._finish(ye, inv, sort_idx, in_splits, out_splits, all_valid, ent, inv_ent if all_valid else None, tok, topk_weights,
+                            T, K, H, x)
+
+    def _finish(self, ye, inv, sort_idx, in_splits, out_splits, all_valid, ent, inv_ent, tok, topk_weights, T, K, H, x):
         y = _PermuteRows.apply(ye, inv, sort_idx)
         back = _AllToAll.apply(y, in_splits, out_splits, self.group)
         if all_valid:
