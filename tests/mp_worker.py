@@ -83,6 +83,30 @@ def main():
             err = (fp8_dequantize(rq, rsc, torch.float32) - want.float()).abs().max().item()
             assert err <= 0.07 * max(1.0, want.float().abs().max().item()), err
         buf.destroy()
+    elif case == "layer_auto":
+        # a shape large enough for the default rules to pick the fused kernels (I >= 1536): no environment switches
+        from teramoe_b200 import engine
+        T, H, I, E, K = 384, 1024, 1536, 2 * world, 2
+        prob = make_problem(world, T, H, I, E, K, seed=9, dtype=dtype, x_scale=0.1, w_scale=0.02, drop_some=True, uneven_tokens=True)
+        ref = oracle(prob)[rank]
+        r = prob["ranks"][rank]
+        El = E // world
+        buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True)
+        outs = []
+        for it in range(2):
+            x = r["x"].to(dev).clone().requires_grad_(True)
+            w = r["w"].to(dev).clone().requires_grad_(True)
+            Wg = prob["W_gateup"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            Wd = prob["W_down"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            out = buf.teramoe_autograd(x, r["idx"].to(dev), w, Wg, Wd, E)
+            out.backward(r["go"].to(dev))
+            outs.append({"out": out.detach(), "dx": x.grad, "dw": w.grad, "dWg": Wg.grad, "dWd": Wd.grad})
+        if dev.type == "cuda":
+            assert buf._engine.last_paths["fused_dispatch_gemm"] and buf._engine.last_paths["fused_combine_fwd"], buf._engine.last_paths
+        compare([outs[0]], [ref], tol, tol)
+        for n in outs[0]:
+            assert torch.equal(outs[0][n], outs[1][n]), f"{n} differs between runs"
+        buf.destroy()
     elif case == "mismatch":
         # ranks disagree on num_experts: the host-side check must raise on every rank, nothing hangs
         buf = tm.Buffer(group, device=dev)

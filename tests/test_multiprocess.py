@@ -59,3 +59,13 @@ def test_nccl_layer_fused_dispatch_and_combine():
     world = torch.cuda.device_count()
     world = 8 if world >= 8 else 4 if world >= 4 else 2
     _launch("nccl", "layer", world, timeout=600, extra_env={"TERAMOE_FUSED_COMBINE": "1", "TERAMOE_FUSED_DISPATCH": "1"})
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_layer_default_rules_pick_fused_kernels():
+    """A shape with I >= 1536 and no environment switches: the default rules must take the fused dispatch + GEMM kernel and
+    the pushed combine, match the fp32 oracle and repeat bit for bit."""
+    world = torch.cuda.device_count()
+    world = 8 if world >= 8 else 4 if world >= 4 else 2
+    _launch("nccl", "layer_auto", world, timeout=600)
