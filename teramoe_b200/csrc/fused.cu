@@ -388,12 +388,8 @@ template <bool B_MN, int EPI>
 cudaError_t launch_fused(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, const FusedArgs& f, int num_sms,
                          cudaStream_t stream) {
     auto kern = fused_dispatch_gemm_kernel<B_MN, EPI>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesF);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[64] = {};
+    if (cudaError_t e = ensure_smem_limit(kern, kSmemBytesF, configured); e != cudaSuccess) return e;
     int grid = num_sms & ~1;
     if (grid < 2 * (f.num_dispatch_clusters + 1)) return cudaErrorInvalidConfiguration;
     // All CTAs must be resident at once (compute pairs wait for rows that dispatch pairs of OTHER ranks send,

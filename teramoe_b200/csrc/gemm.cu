@@ -245,12 +245,8 @@ template <bool A_MN, bool B_MN, bool KGROUP, int EPI, int GATHER>
 cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms,
                    cudaStream_t stream) {
     auto kern = grouped_gemm_kernel<A_MN, B_MN, KGROUP, EPI, GATHER>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[64] = {};
+    if (cudaError_t e = ensure_smem_limit(kern, kSmemBytes, configured); e != cudaSuccess) return e;
     if (total_tiles <= 0) return cudaSuccess;
     int grid = total_tiles < num_sms ? total_tiles : num_sms;
     kern<<<grid, kThreads, kSmemBytes, stream>>>(ma, mb, g);

@@ -302,12 +302,8 @@ template <bool A_MN, bool B_MN, bool KGROUP, int EPI>
 cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& g, int total_tiles, int num_sms, cudaStream_t stream) {
     auto kern = grouped_gemm2_kernel<A_MN, B_MN, KGROUP, EPI>;
     constexpr int kSmemBytes2 = smem_bytes_for(EPI);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[64] = {};
+    if (cudaError_t e = ensure_smem_limit(kern, kSmemBytes2, configured); e != cudaSuccess) return e;
     if (total_tiles <= 0) return cudaSuccess;
     int grid = 2 * total_tiles < num_sms ? 2 * total_tiles : num_sms;
     grid &= ~1;

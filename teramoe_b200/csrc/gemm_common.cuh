@@ -253,6 +253,18 @@ inline cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, u
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// The dynamic shared-memory limit of a kernel is a per-device attribute: set it once on every device that launches it.
+template <typename Kernel>
+inline cudaError_t ensure_smem_limit(Kernel kern, int bytes, bool (&done)[64]) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    return e;
+}
+
 inline int default_sms(int num_sms) {
     if (num_sms > 0) return num_sms;
     static int cached = 0;
