@@ -6,6 +6,11 @@ Backward re-uses the forward layout (slots are deterministic): dispatch grad row
 expand, grad_act GEMM + dSwiGLU, dX GEMM, two weight-gradient GEMMs, combine push (+ route-weight
 gradients) -> [barrier] -> reduce.
 
+For large shapes the default collapses these phases into fused kernels: "dispatch push -> barrier -> expand ->
+first GEMM" becomes ONE cooperative kernel (csrc/fused.cu: dispatch CTA pairs feed compute CTA pairs through
+per-block arrival counters, then join them), and "second GEMM -> combine push" becomes the GEMM with the
+push epilogue (csrc/gemm2.cu, kEpiPush).  The switches and the measured rules are below.
+
 Kept for backward, as in the reference (csrc/teramoe/teramoe_orchestrator.cu:3653-3678): the
 dispatched X once per received token, the (gate, up) pre-activation per slot, and the slot tables.
 `act` is recomputed from the pre-activation.
