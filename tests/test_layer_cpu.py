@@ -55,3 +55,24 @@ def test_argument_validation():
         buf.destroy()  # explicitly_destroy not set
     with pytest.raises(ValueError):
         tm.Buffer(None, num_nvl_bytes=100, device="cpu")
+
+
+def test_fused_path_rules(monkeypatch):
+    """The default rules that pick the fused kernels are pure functions of the shape, the rank count and the table size,
+    so every rank takes the same decision."""
+    from teramoe_b200 import engine
+    monkeypatch.setattr(engine, "_FUSED_DISPATCH_MODE", "auto")
+    monkeypatch.setattr(engine, "_FUSED_MODE", "auto")
+    monkeypatch.setattr(engine, "USE_CTA_PAIRS", True)
+    monkeypatch.setattr(engine, "USE_TMA_GATHER", False)
+    assert engine.use_fused_dispatch(2048, 8, 1 << 30) and engine.use_fused_dispatch(2048, 1, 1 << 30)
+    assert not engine.use_fused_dispatch(512, 8, 1 << 30)                 # the GEMM is shorter than the transfer
+    assert not engine.use_fused_dispatch(2048, 8, 12 * (1 << 30))         # operand table too large for the arena
+    assert engine.use_fused_combine(2048, 8, False) and engine.use_fused_combine(1024, 8, True)
+    assert not engine.use_fused_combine(1024, 8, False) and engine.use_fused_combine(256, 1, False)
+    monkeypatch.setattr(engine, "_FUSED_DISPATCH_MODE", "0")
+    assert not engine.use_fused_dispatch(2048, 8, 0)
+    # num_dispatch_sms -> CTA pairs that dispatch first (two SMs per pair) unless the environment fixes them
+    monkeypatch.setattr(engine, "_pairs_env", None)
+    assert engine.dispatch_pairs(0, 32) == 16 and engine.dispatch_pairs(1, 2) == 2 and engine.dispatch_pairs(0, 400) == 48
+    assert engine.dispatch_pairs(0, 0) == engine.FUSED_DISPATCH_CLUSTERS[0]
