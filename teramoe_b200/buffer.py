@@ -144,7 +144,8 @@ class Buffer(LowLatencyMixin):
     def state(self) -> dict:
         """Sizes and configuration needed to rebuild an equivalent Buffer (nothing else persists between calls)."""
         return {"rank": self.rank, "group_size": self.group_size, "device": str(self.device), "num_nvl_bytes": self.num_nvl_bytes,
-                "arena_bytes": self._world.data_bytes, "num_sms": Buffer.num_sms, "low_latency_mode": self.low_latency_mode}
+                "arena_bytes": self._world.data_bytes, "num_sms": Buffer.num_sms, "low_latency_mode": self.low_latency_mode,
+                "last_paths": dict(getattr(self._engine, "last_paths", {}))}      # which fused kernels the last layer call used
 
     # ------------------------------------------------------------------ knobs
     @staticmethod
