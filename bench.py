@@ -95,6 +95,8 @@ def main():
         T = args.tokens
     N = world
     E = El * N
+    if K > E:
+        raise SystemExit(f"config {args.config}: top-{K} routing needs at least {K} experts, {N} rank(s) x {El} give {E}; use more GPUs")
     gen = torch.Generator().manual_seed(1234 + rank)
     x_host = (torch.randn(T, H, generator=gen)).to(torch.bfloat16).pin_memory()
     go_host = (torch.randn(T, H, generator=gen)).to(torch.bfloat16).pin_memory()
