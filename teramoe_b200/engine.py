@@ -78,7 +78,7 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 # the transfer (same rule as the fused combine, which it requires) and the slot-space operand table, which
 # then lives in the symmetric arena, stays under FUSED_DISPATCH_MAX_BYTES.
 # Measured (H=7168, I=2048, top-8, 8192 tokens/rank, step ms fused / separate on the same box):
-# EP=1 16.0 / 16.5 and 16.3 / 17.0 (two boxes' clocks), EP=2 17.0 / 17.4, EP=8 19.0 / 19.1.
+# EP=1 16.0 / 16.5 and 16.3 / 17.0 (two boxes' clocks), EP=2 17.0 / 17.4, EP=4 17.2 / 17.4, EP=8 19.0 / 19.1.
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "auto")
 FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "4e9")))
 # CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
