@@ -133,6 +133,16 @@ class Buffer(LowLatencyMixin):
             raise RuntimeError("Buffer was destroyed")
         return self._world.drive(gen)
 
+    def check_status(self) -> None:
+        """Wait for the kernels enqueued so far and raise if a device-side wait of any of them ran out.  Every call
+        on the buffer looks at the snapshots of the calls before it without waiting; this is the blocking form, for
+        the end of a step or of a run."""
+        self._world.check_status()
+
+    def set_wait_limit_ms(self, ms: int) -> None:
+        """Limit of the device-side waits on other ranks (default 30 s; 0 restores it)."""
+        self._world.set_wait_limit_ms(ms)
+
     def trace(self, on: bool = True) -> None:
         """Start / stop recording per-phase device times of the fused layer calls (CUDA events)."""
         self._engine.enable_trace(on)

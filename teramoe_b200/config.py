@@ -32,13 +32,17 @@ class Config:
     num_max_rdma_chunked_recv_tokens: int = 256
 
     def __post_init__(self):
-        if self.num_sms <= 0:
-            raise ValueError("num_sms must be positive")
+        # the reference's invariants (csrc/config.hpp:56-76)
+        if self.num_sms < 0:
+            raise ValueError("num_sms must not be negative")
         if not (0 < self.num_max_nvl_chunked_send_tokens < self.num_max_nvl_chunked_recv_tokens):
             raise ValueError("need 0 < nvl send chunk < nvl recv chunk")
-        if not (0 < self.num_max_rdma_chunked_send_tokens <= self.num_max_rdma_chunked_recv_tokens // 2 + 1
-                or self.num_max_rdma_chunked_send_tokens < self.num_max_rdma_chunked_recv_tokens):
-            raise ValueError("need rdma send chunk < rdma recv chunk")
+        if self.num_max_rdma_chunked_send_tokens <= 0 or self.num_max_rdma_chunked_recv_tokens <= 0:
+            raise ValueError("rdma chunk sizes must be positive")
+        send, recv = self.num_max_rdma_chunked_send_tokens, self.num_max_rdma_chunked_recv_tokens
+        self.num_max_rdma_chunked_recv_tokens = recv = (recv + send - 1) // send * send     # rounded up to whole send chunks
+        if not (send < recv and send <= recv // 2):
+            raise ValueError("need rdma send chunk <= rdma recv chunk / 2")
 
     def get_nvl_buffer_size_hint(self, hidden_bytes: int, num_ranks: int) -> int:
         """Bytes of symmetric memory that comfortably hold one dispatch + one combine of

@@ -33,7 +33,7 @@ void check_f32(const torch::Tensor& t, const char* name) {
 int* status_ptr(const c10::optional<torch::Tensor>& status) {
     if (!status.has_value()) return nullptr;
     check_i32(*status, "status");
-    TORCH_CHECK(status->numel() >= 4, "status must hold 4 ints");
+    TORCH_CHECK(status->numel() >= 8, "status must hold 8 ints");
     return status->data_ptr<int>();
 }
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
@@ -179,6 +179,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("gemm_bwd_dx", &gemm_bwd_dx);
     m.def("gemm_wgrad", &gemm_wgrad);
     m.def("gemm_num_droute_parts", &tmoe::gemm_num_droute_parts);
+    m.def("gemm_has_gather4", &tmoe::gemm_has_gather4);
     m.def("launch_count", [] { return tmoe::launch_counter().load(); });
     register_more(m);
 }

@@ -40,7 +40,11 @@ void* bf16(const torch::Tensor& t, const char* name) {
     return t.data_ptr();
 }
 void check_i32(const torch::Tensor& t, const char* name) { (void)i32(t, name); }
-int* opt_status(const c10::optional<torch::Tensor>& s) { return s.has_value() ? i32(*s, "status") : nullptr; }
+int* opt_status(const c10::optional<torch::Tensor>& s) {
+    if (!s.has_value()) return nullptr;
+    TORCH_CHECK(s->numel() >= 8, "status must hold 8 ints");
+    return i32(*s, "status");
+}
 
 struct TopK {
     const void* ptr;

@@ -332,7 +332,7 @@ int grid_for_warps(long warps, int block) {
 
 cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms,
                        cudaStream_t stream) {
-    const uint64_t limit_ns = limit_ms > 0 ? (uint64_t)limit_ms * 1000000ull : TMOE_WAIT_LIMIT_NS;
+    const uint64_t limit_ns = limit_ms > 0 ? (uint64_t)limit_ms * 1000000ull : 0ull;   // 0: the status block's run-time limit
     ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns);
     return cudaGetLastError();
 }

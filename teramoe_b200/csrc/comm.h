@@ -18,7 +18,7 @@ struct SymOffsets {
     uint64_t gtw;        // [tok_cap*K] float   route-weight gradients arriving from expert ranks
 };
 
-// limit_ms <= 0 selects the default wait limit (2 s).
+// limit_ms <= 0 selects the run-time limit of the status block (ptx.cuh).
 cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms,
                        cudaStream_t stream);
 

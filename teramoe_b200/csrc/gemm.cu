@@ -253,6 +253,14 @@ cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs&
     return cudaGetLastError();
 }
 
+// The TMA tile::gather4 operand modes measured about three times slower than a dense slot-space operand, so their
+// kernels are only compiled when the library is built with -DTMOE_WITH_GATHER4; otherwise asking for them is an error.
+#ifdef TMOE_WITH_GATHER4
+#define TMOE_GATHER_LAUNCH(call) call
+#else
+#define TMOE_GATHER_LAUNCH(call) cudaErrorNotSupported
+#endif
+
 void set_push(GemmArgs& g, const PushTarget& p) {
     g.push_ptrs = reinterpret_cast<const unsigned long long*>(p.arena_ptrs);
     g.push_off = p.landing_off;
@@ -301,7 +309,7 @@ cudaError_t gemm_fwd_gateup(const void* xperm, const void* w_gateup, void* act, 
     if (lay.unit_blk != nullptr && gather_rows == nullptr)
         return gemm2_mgroup(0, xperm, w_gateup, g, max_mblocks * BM, H, num_local_experts * 2 * I, H, num_sms, stream);
     if (gather_rows != nullptr)
-        return launch<false, false, false, kEpiSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+        return TMOE_GATHER_LAUNCH((launch<false, false, false, kEpiSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream)));
     return launch<false, false, false, kEpiSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
@@ -376,7 +384,7 @@ cudaError_t gemm_bwd_gradact(const void* dyperm, const void* w_down, const void*
     if (lay.unit_blk != nullptr && gather_rows == nullptr)
         return gemm2_mgroup(2, dyperm, w_down, g, max_mblocks * BM, H, num_local_experts * H, I, num_sms, stream);
     if (gather_rows != nullptr)
-        return launch<false, true, false, kEpiDSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
+        return TMOE_GATHER_LAUNCH((launch<false, true, false, kEpiDSwiGLU, 1>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream)));
     return launch<false, true, false, kEpiDSwiGLU, 0>(ma, mb, g, max_mblocks * g.num_n_blocks, default_sms(num_sms), stream);
 }
 
@@ -441,9 +449,17 @@ cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_of
     g.gather_rows = gather_rows;
     const int tiles = num_local_experts * g.max_mblocks * g.num_n_blocks;
     if (cta_pairs && gather_operand == 0 && total_rows > 0) return gemm2_wgrad(a, b, g, total_rows, M, N, num_sms, stream);
-    if (gather_operand == 1) return launch<true, true, true, kEpiStore, 1>(ma, mb, g, tiles, default_sms(num_sms), stream);
-    if (gather_operand == 2) return launch<true, true, true, kEpiStore, 2>(ma, mb, g, tiles, default_sms(num_sms), stream);
+    if (gather_operand == 1) return TMOE_GATHER_LAUNCH((launch<true, true, true, kEpiStore, 1>(ma, mb, g, tiles, default_sms(num_sms), stream)));
+    if (gather_operand == 2) return TMOE_GATHER_LAUNCH((launch<true, true, true, kEpiStore, 2>(ma, mb, g, tiles, default_sms(num_sms), stream)));
     return launch<true, true, true, kEpiStore, 0>(ma, mb, g, tiles, default_sms(num_sms), stream);
+}
+
+bool gemm_has_gather4() {
+#ifdef TMOE_WITH_GATHER4
+    return true;
+#else
+    return false;
+#endif
 }
 
 }  // namespace tmoe

@@ -78,4 +78,7 @@ cudaError_t gemm_wgrad(const void* a, const void* b, void* dw, const int* seg_of
 
 int gemm_num_droute_parts(int I);
 
+// Whether the TMA row-gather operand modes were compiled in (-DTMOE_WITH_GATHER4).
+bool gemm_has_gather4();
+
 }  // namespace tmoe

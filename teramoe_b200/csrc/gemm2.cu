@@ -31,7 +31,7 @@ namespace {
 
 // Pipeline depth: six 32 KB stages; the push epilogue gives one stage up for its staging buffers.
 __host__ __device__ constexpr int stages_for(int epi) { return epi == kEpiPush ? 5 : 6; }
-constexpr int kPushRowBytes = 128 + 16;                        // 64 bf16 columns + pad (bank-conflict-free rows)
+constexpr int kPushRowBytes = 128 + 16;                        // 64 bf16 columns + pad (bank-conflict-free rows, 16-byte aligned)
 constexpr int kPushWarpBytes = 32 * kPushRowBytes;             // one epilogue warp stages 32 rows x 64 columns
 __host__ __device__ constexpr int smem_bytes_for(int epi) {
     return stages_for(epi) * (16384 + 16384) + 1024 + 256 + (epi == kEpiPush ? kEpiWarps * kPushWarpBytes : 0);
@@ -234,8 +234,10 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
             if constexpr (EPI == kEpiPush) {
                 // Combine fused into the GEMM: this warp's 32 rows x 128 columns leave for the ranks that own the
-                // tokens.  Rows are staged in shared memory 64 columns at a time so that every store
-                // instruction writes four 128-byte row segments (coalesced peer stores over NVLink).
+                // tokens.  Each lane stages its row in shared memory 64 columns (128 bytes) at a time and hands the
+                // segment to a bulk copy shared -> peer global, so no thread of the epilogue waits for NVLink: the
+                // warp goes straight back to draining tensor memory, and only re-using the staging row waits until
+                // the copy engine has READ it (cp.async.bulk.wait_group.read), not until the peer has the bytes.
                 unsigned long long dst_row = 0ull;
                 if (live) {
                     const int tk = g.slot_tk[row];
@@ -250,6 +252,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 const uint32_t my_row_smem = my_stage + (uint32_t)lane * kPushRowBytes;
 #pragma unroll 1
                 for (int cg = 0; cg < 2; ++cg) {
+                    tma_store_wait_read<0>();          // this lane's previous segment has left shared memory
 #pragma unroll
                     for (int c2 = 0; c2 < 2; ++c2) {
                         uint32_t acc[32];
@@ -265,21 +268,12 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                          "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
                         }
                     }
-                    __syncwarp();
                     const int col0 = n0 + cg * 64;
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rsel = it * 4 + (lane >> 3);
-                        const int seg = lane & 7;
-                        const unsigned long long p = __shfl_sync(0xffffffffu, dst_row, rsel);
-                        if (p != 0ull && col0 + seg * 8 + 8 <= g.n_total) {
-                            int4 v;
-                            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                                         : "r"(my_stage + (uint32_t)rsel * kPushRowBytes + (uint32_t)seg * 16));
-                            st_na_v4(reinterpret_cast<void*>(p + (unsigned long long)(col0 + seg * 8) * 2ull), v);
-                        }
+                    if (dst_row != 0ull && col0 + 64 <= g.n_total) {
+                        fence_proxy_async_smem();      // this lane's generic-proxy stores -> the bulk copy's read
+                        bulk_store_1d(dst_row + (unsigned long long)col0 * 2ull, my_row_smem, 128u);
                     }
-                    __syncwarp();
+                    tma_store_commit();
                 }
             } else {
                 if (live) epilogue_thread<EPI>(g, taddr0, row_ok ? row : 0, row_ok, n0, tile.n_blk * 2 + h, tile.nk == 0);
@@ -288,6 +282,7 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(as), 0));
         }
+        if constexpr (EPI == kEpiPush) tma_store_wait<0>();   // every pushed segment of this lane has been written
     }
 
     tcgen05_fence_before();
@@ -326,6 +321,8 @@ cudaError_t gemm2_mgroup(int kind, const void* a, const void* b, const GemmArgs&
         return e;
     const int tiles = g.max_units * g.num_n_blocks;
     const int sms = default_sms(num_sms);
+    // the push epilogue hands whole 128-byte segments (64 columns) to bulk copies: 16-byte aligned rows, no ragged edge
+    if ((kind == 4 || kind == 5) && (g.n_total % 64 != 0 || g.ldd % 8 != 0 || g.push_off % 16 != 0)) return cudaErrorInvalidValue;
     switch (kind) {
         case 0: return launch2<false, false, false, kEpiSwiGLU>(ma, mb, g, tiles, sms, stream);
         case 1: return launch2<false, false, false, kEpiStore>(ma, mb, g, tiles, sms, stream);

@@ -76,13 +76,14 @@ extern "C" __attribute__((visibility("default"))) int tmoe_route_counts_noalloc(
     if (num_tokens < 0 || top_k <= 0 || num_experts <= 0 || num_ranks <= 0 || num_experts % num_ranks != 0)
         return fail(TMOE_NOALLOC_BAD_ARGUMENT, err, err_len, "need T >= 0, K > 0, E > 0, N > 0 and E divisible by N");
     const int C = num_experts + num_ranks + 2;
-    const int chunks = (num_tokens + kChunkTokens - 1) / kChunkTokens;
-    if (chunks > kMaxChunks || C > kMaxCols || top_k > 32 || num_ranks > 32) {
+    // compare the token count itself: rounding it up to chunks first could overflow an int near INT_MAX
+    if (num_tokens > kMaxChunks * kChunkTokens || C > kMaxCols || top_k > 32 || num_ranks > 32) {
         char msg[200];
         snprintf(msg, sizeof(msg), "size beyond the built-in scratch: limits are T <= %d, K <= 32, N <= 32, E + N + 2 <= %d (got T=%d K=%d N=%d E=%d)",
                  kMaxChunks * kChunkTokens, kMaxCols, num_tokens, top_k, num_ranks, num_experts);
         return fail(TMOE_NOALLOC_TOO_LARGE, err, err_len, msg);
     }
+    const int chunks = (num_tokens + kChunkTokens - 1) / kChunkTokens;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(TMOE_NOALLOC_CUDA_ERROR, err, err_len, cudaGetErrorString(e));

@@ -20,8 +20,10 @@
 namespace tmoe {
 
 // ---------------------------------------------------------------------------------------------
-// Status block (one per launch, in global memory, zeroed by the host before the launch).
+// Status block (one per rank, in global memory, 8 ints; words 0-3 are zero while all is well).
 // word 0: first error code (0 = ok)   word 1: site id   word 2: block index   word 3: detail
+// words 4-5: limit in ns (64 bit) of the waits on OTHER ranks (barriers, arrival counters); 0 selects
+//            the built-in default.  The host sets it (EPWorld.set_wait_limit_ms), kernels only read it.
 // ---------------------------------------------------------------------------------------------
 enum StatusCode : int {
     kStatusOk = 0,
@@ -41,9 +43,22 @@ __device__ __forceinline__ void report_status(int* status, int code, int site, i
     }
 }
 
+// Waits inside one CTA or CTA pair (mbarriers): 2 s is far beyond any healthy pipeline stall.
 #ifndef TMOE_WAIT_LIMIT_NS
-#define TMOE_WAIT_LIMIT_NS 2000000000ull  // 2 s: generous for a layer step, short enough to never wedge a shared GPU
+#define TMOE_WAIT_LIMIT_NS 2000000000ull
 #endif
+// Waits on another rank see that rank's skew (a checkpoint write, a slow data loader, a first-step build), so
+// their limit is a run-time value read from the status block; this is the default when none is set.
+// The reference budgets about 100 s for the same waits (csrc/kernels/configs.cuh:20-26).
+#ifndef TMOE_PEER_WAIT_LIMIT_NS
+#define TMOE_PEER_WAIT_LIMIT_NS 30000000000ull
+#endif
+
+__device__ __forceinline__ uint64_t peer_wait_limit_ns(const int* status) {
+    if (status == nullptr) return TMOE_PEER_WAIT_LIMIT_NS;
+    const uint64_t v = *reinterpret_cast<const volatile uint64_t*>(status + 4);
+    return v != 0ull ? v : TMOE_PEER_WAIT_LIMIT_NS;
+}
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
@@ -416,9 +431,10 @@ __device__ __forceinline__ void warp_copy_row(int4* dst, const int4* src, int nv
 }
 
 // Bounded wait until *flag >= target (acquire, system scope).  One thread calls it.
-__device__ __forceinline__ bool wait_flag_ge_sys(const int* flag, int target, int* status, int site,
-                                                 uint64_t limit_ns = TMOE_WAIT_LIMIT_NS) {
+// limit_ns == 0: the run-time limit for waits on other ranks (status block words 4-5, else the default).
+__device__ __forceinline__ bool wait_flag_ge_sys(const int* flag, int target, int* status, int site, uint64_t limit_ns = 0ull) {
     if (ld_acquire_sys(flag) >= target) return true;
+    if (limit_ns == 0ull) limit_ns = peer_wait_limit_ns(status);
     const uint64_t t0 = globaltimer_ns();
 #pragma unroll 1
     while (true) {

@@ -37,7 +37,8 @@ from .parallel.world import EPWorld, _round_up
 # Feed the GEMMs through TMA row gather (tile::gather4) instead of an expanded slot-space copy.
 # Measured on B200 (H=7168, I=2048, 65,536 slot rows): gather4 sustains about one 4-row x 128-byte
 # copy per ~70 cycles per SM, which caps the gate_up GEMM at 457 TFLOP/s against 1400 with a dense
-# operand, while the expand pass costs 0.3 ms.  So the expanded copy is the default.
+# operand, while the expand pass costs 0.3 ms.  So the expanded copy is the default, and the gather kernels are only
+# compiled when the extension is built with -DTMOE_WITH_GATHER4 (the switch raises otherwise).
 USE_TMA_GATHER = os.environ.get("TERAMOE_TMA_GATHER", "0") == "1"
 # CTA-pair (tcgen05 cta_group::2, 256x256 tiles) GEMM kernels: bitwise equal to the one-CTA 128x256
 # kernels and 6-27 % faster (csrc/gemm2.cu).  "0" selects the one-CTA kernels.
@@ -150,7 +151,7 @@ class SavedForBackward:
     stats: dict = field(default_factory=dict)
 
 
-def _arena_geometry(maxima, H: int, K: int, fused_dispatch: bool = False):
+def _table_sizes(maxima, H: int, K: int):
     rmax, smax, lmax, tmax = [max(int(v), 1) for v in maxima]
     lmax = max(lmax, tmax * K)      # the fused combine lands one row per (token, k) entry
     smax = (smax + 127) // 128 * 128
@@ -160,6 +161,11 @@ def _arena_geometry(maxima, H: int, K: int, fused_dispatch: bool = False):
         "landing": lmax * H * 2, "gtw": tmax * K * 4,
         "slot_x": smax * H * 2, "row_first": rmax * 4,
     }
+    return sizes, (rmax, smax, lmax, tmax)
+
+
+def _arena_geometry(maxima, H: int, K: int, fused_dispatch: bool = False):
+    sizes, (rmax, smax, lmax, tmax) = _table_sizes(maxima, H, K)
     offs, off = {}, 0
     for name in TABLES + (EXTRA_TABLES if fused_dispatch else ()):
         offs[name] = off
@@ -206,6 +212,29 @@ class EPEngine:
             prev = ev
         self._trace = []
         return {k: acc[k] / cnt[k] for k in acc}
+
+    # ------------------------------------------------------------------ arena reuse between calls
+    # Peers store into this rank's arena; the arena is reused by every call.  What makes that safe:
+    #  (1) every read of a table in a call is stream-ordered before the call's last barrier signal, except the reads
+    #      registered with `_late` (the reduce of the landed rows, the clones of an un-fused dispatch);
+    #  (2) a peer writes a table in its NEXT call either after a barrier of that call (forward: the count exchange), or
+    #      rows that this rank asked for in that same call (combine pushes answer this rank's own dispatch, which it
+    #      issued after its late reads), or, for the remaining case, pushes without a barrier first (backward
+    #      dispatch, cached-handle dispatch, un-fused combine), after `_entry_barrier` found no overlap between what is
+    #      about to be written and the registered late reads (same layer, same geometry: disjoint tables) or crossed
+    #      one more barrier.
+    def _ranges(self, h: LayerHandle, H: int, offs, names):
+        sizes, _ = _table_sizes(h.maxima, H, h.K)
+        return [(offs[n], sizes[n]) for n in names if n in offs]
+
+    def _late(self, h: LayerHandle, H: int, offs, names) -> None:
+        if self.is_cuda:
+            for off, n in self._ranges(h, H, offs, names):
+                self.world.note_late_read(off, n)
+
+    def _entry_barrier(self, h: LayerHandle, H: int, offs, names):
+        if self.is_cuda and self.world.size > 1 and self.world.needs_entry_barrier(self._ranges(h, H, offs, names)):
+            yield ("barrier",)
 
     # ------------------------------------------------------------------ table access
     def _tables(self, offs, maxima, H, K, dtype):
@@ -308,6 +337,8 @@ class EPEngine:
         if self.is_cuda:
             yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, x.dtype)
+        pushed = ("recv_x",) + (("slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots") if with_meta else ())
+        yield from self._entry_barrier(h, H, offs, pushed)
         if self.is_cuda:
             ext = self.ext
             if with_meta:
@@ -327,6 +358,7 @@ class EPEngine:
         self._mark("  dispatch push kernel")
         yield ("barrier",)
         self._mark("  dispatch barrier")
+        self._late(h, H, offs, pushed)        # the caller reads (clones, expands) these after the barrier
         return tabs, offs
 
     def snapshot_tables(self, h: LayerHandle, tabs) -> None:
@@ -384,12 +416,14 @@ class EPEngine:
     def combine_gen(self, h: LayerHandle, y: torch.Tensor, tabs, offs, droute_parts: Optional[torch.Tensor] = None):
         """Sum each received token's local expert outputs and push one row back to its source; after
         the barrier reduce the landed rows.  -> (out [T,H], gtw [T,K] or None)."""
+        yield from self._entry_barrier(h, h.H, offs, ("landing", "gtw"))
         writes = self._combine_push(h, y, offs, droute_parts)
         if writes is not None:
             yield ("push", writes)
         self._mark("  combine push kernel")
         yield ("barrier",)
         self._mark("  combine barrier")
+        self._late(h, h.H, offs, ("landing", "gtw"))
         res = self._combine_reduce(h, tabs, y.dtype, y.device, droute_parts is not None)
         self._mark("  combine reduce kernel")
         return res
@@ -414,6 +448,7 @@ class EPEngine:
         hh.row_slots = torch.full((R, K), -1, dtype=torch.int32, device=dev)
         if R:
             hh.row_slots[:, 0] = torch.arange(R, dtype=torch.int32, device=dev)
+        yield from self._entry_barrier(hh, hh.H, offs, ("landing", "gtw"))
         writes = [self._combine_push(hh, x.contiguous(), offs, None)]
         if recv_topk_weights is not None:
             # the side channel is indexed by slot: scatter the received weights into slot space
@@ -428,6 +463,7 @@ class EPEngine:
             if wri is not None:
                 yield ("push", wri)
         yield ("barrier",)
+        self._late(hh, hh.H, offs, ("landing", "gtw"))
         return self._combine_reduce(hh, tabs, x.dtype, dev, recv_topk_weights is not None)
 
     def slots_combine_gen(self, h: LayerHandle, y: torch.Tensor, weights: Optional[torch.Tensor]):
@@ -440,6 +476,7 @@ class EPEngine:
         if self.is_cuda:
             yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, y.dtype)
+        yield from self._entry_barrier(h, H, offs, ("landing",))
         if self.is_cuda:
             if h.slots > 0:
                 self.ext.slot_rows_push(y.contiguous(), h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"),
@@ -454,6 +491,7 @@ class EPEngine:
                 writes[s] = [("landing", h.slot_tk.long()[valid[m]], y[valid[m]])]
             yield ("push", writes)
         yield ("barrier",)
+        self._late(h, H, offs, ("landing",))
         out = torch.empty(T, H, dtype=y.dtype, device=y.device)
         if T == 0:
             return out
@@ -527,6 +565,7 @@ class EPEngine:
             self._mark("fwd:down GEMM + pushed combine")
             yield ("barrier",)
             self._mark("fwd:combine barrier")
+            self._late(h, H, offs, ("landing",))
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             if T > 0:
                 self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out, None)
@@ -562,6 +601,7 @@ class EPEngine:
         offs, total, maxima = _arena_geometry(h.maxima, H, K, True)
         yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, rows_in.dtype)
+        yield from self._entry_barrier(h, H, offs, ("slot_x", "slot_w", "slot_tk", "slot_row", "row_first"))
         S = h.slots
         dev = rows_in.device
         if kind == 0:
@@ -686,6 +726,7 @@ class EPEngine:
             # weight gradients were enqueued after the push so they overlap the other ranks' pushes
             yield ("barrier",)
             self._mark("bwd:combine barrier")
+            self._late(h, h.H, offs, ("landing", "gtw"))
             T, K = h.T, h.K
             dx = torch.empty(T, h.H, dtype=grad_out.dtype, device=grad_out.device)
             if T > 0:

@@ -25,6 +25,8 @@ from typing import Dict, Generator, List, Optional
 import torch
 import torch.distributed as dist
 
+STATUS_RING = 64                 # status snapshots in flight before the oldest is waited for
+STRICT_STATUS = os.environ.get("TERAMOE_STRICT_STATUS", "0") == "1"
 CONTROL_ROW_INTS = 8192          # capacity of one metadata row (E + ranks + 2 ints must fit)
 MAX_BLOCKS = 65536               # per-block arrival counters of the fused dispatch (8.4 M slot rows)
 _ALIGN = 256
@@ -57,8 +59,18 @@ class EPWorld:
             self.control_bytes = _round_up(self.blk_cnt_offset + MAX_BLOCKS * 4 + 4096)
             with torch.cuda.device(self.device):
                 self.control = self.ext.SymmetricArena(rank, size, self.control_bytes)
-            self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+            # status block (csrc/ptx.cuh): words 0-3 error record, words 4-5 the limit (ns) of waits on other ranks
+            self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
             self.sizes_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+            self._status_ring = torch.zeros(STATUS_RING, 4, dtype=torch.int32).pin_memory()
+            self._status_pending: list = []          # (ring row, event) of status snapshots not looked at yet
+            self._status_next = 0
+            ms = int(os.environ.get("TERAMOE_PEER_WAIT_LIMIT_MS", "0"))
+            if ms > 0:
+                self.set_wait_limit_ms(ms)
+        self.strict_status = STRICT_STATUS
+        # byte ranges of the data arena that the previous call still reads after its last barrier
+        self._late_reads: List[tuple] = []
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -133,15 +145,79 @@ class EPWorld:
         return self.epoch
 
     # ------------------------------------------------------------------ drivers
+    def set_wait_limit_ms(self, ms: int) -> None:
+        """Limit of every device-side wait on ANOTHER rank (barriers, arrival counters), in milliseconds; 0 restores
+        the built-in default (30 s; the reference budgets about 100 s, csrc/kernels/configs.cuh:20-26).  Waits inside
+        one CTA pair keep their fixed 2 s."""
+        if self.is_cuda:
+            self.status[4:6].view(torch.int64).fill_(int(ms) * 1_000_000)
+
+    def _raise_status(self, s) -> None:
+        self.status[:4].zero_()
+        self._status_pending.clear()
+        names = {1: "mbarrier wait", 2: "flag wait", 3: "barrier", 4: "bad argument"}
+        raise RuntimeError(f"teramoe_b200: a device-side wait ran out on rank {self.rank}: {names.get(s[0], s[0])} "
+                           f"(site {s[1]}, block {s[2]}, detail {s[3]})")
+
     def check_status(self) -> None:
+        """Blocking read of the status block; raises if a device-side wait of any earlier kernel ran out."""
         if not self.is_cuda:
             return
-        s = self.status.tolist()
+        s = self.status[:4].tolist()
+        self._status_pending.clear()
         if s[0] != 0:
-            self.status.zero_()
-            names = {1: "mbarrier wait", 2: "flag wait", 3: "barrier", 4: "bad argument"}
-            raise RuntimeError(f"teramoe_b200: a device-side wait ran out on rank {self.rank}: {names.get(s[0], s[0])} "
-                               f"(site {s[1]}, block {s[2]}, detail {s[3]})")
+            self._raise_status(s)
+
+    def note_status(self, strict: Optional[bool] = None) -> None:
+        """End of a call: snapshot the status block into pinned memory behind the call's kernels (16 bytes, no host
+        wait).  Snapshots are looked at by poll_status (every later call does that first) and by check_status; with
+        `strict` (or TERAMOE_STRICT_STATUS=1) the host waits for this snapshot, so the call whose wait ran out is the one
+        that raises, at the price of one stream wait per call."""
+        if not self.is_cuda:
+            return
+        if len(self._status_pending) >= STATUS_RING:
+            row, ev = self._status_pending.pop(0)
+            ev.synchronize()
+            if int(self._status_ring[row, 0]) != 0:
+                self._raise_status(self._status_ring[row].tolist())
+        row = self._status_next
+        self._status_next = (row + 1) % STATUS_RING
+        self._status_ring[row].copy_(self.status[:4], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._status_pending.append((row, ev))
+        if self.strict_status if strict is None else strict:
+            ev.synchronize()
+        self.poll_status()
+
+    def poll_status(self) -> None:
+        """Look at the snapshots whose copies have completed; never waits."""
+        if not self.is_cuda:
+            return
+        while self._status_pending and self._status_pending[0][1].query():
+            row, _ = self._status_pending.pop(0)
+            if int(self._status_ring[row, 0]) != 0:
+                self._raise_status(self._status_ring[row].tolist())
+
+    # ------------------------------------------------------------------ arena reuse between calls
+    def note_late_read(self, offset: int, nbytes: int) -> None:
+        """The current call reads [offset, offset+nbytes) of the data arena AFTER its last barrier."""
+        if nbytes > 0:
+            self._late_reads.append((int(offset), int(offset) + int(nbytes)))
+
+    def passed_barrier(self) -> None:
+        self._late_reads.clear()
+
+    def needs_entry_barrier(self, write_ranges) -> bool:
+        """A call is about to let peers write `write_ranges` [(offset, nbytes)] of this rank's arena without having
+        crossed a barrier first.  That is safe only if no rank can still be reading those bytes from the previous call:
+        every read of a call is ordered before the call's last barrier signal except the ones registered with
+        note_late_read.  All ranks run the same calls with the same geometry, so they all answer the same."""
+        for off, n in write_ranges:
+            for lo, hi in self._late_reads:
+                if off < hi and lo < off + n:
+                    return True
+        return False
 
     def device_barrier(self, site: int = 500, limit_ms: int = 0) -> None:
         """Bounded all-rank barrier kernel on the current stream (limit_ms <= 0: the default 2 s)."""
@@ -154,6 +230,7 @@ class EPWorld:
     def drive(self, gen: Generator):
         """Run a pipeline generator to completion in real (one process per rank) mode."""
         assert self.virtual_peers is None
+        self.poll_status()
         try:
             req = next(gen)
             while True:
@@ -163,6 +240,7 @@ class EPWorld:
                         self.device_barrier()
                     else:
                         self._cpu_exchange_pushes()
+                    self.passed_barrier()
                     req = gen.send(None)
                 elif kind == "allgather":
                     t = req[1]
@@ -183,6 +261,7 @@ class EPWorld:
                 else:
                     raise RuntimeError(f"unknown pipeline request {kind}")
         except StopIteration as stop:
+            self.note_status()
             return stop.value
 
     def _cpu_exchange_pushes(self) -> None:
@@ -207,6 +286,11 @@ class EPWorld:
         self.closed = True
         if self.is_cuda:
             torch.cuda.synchronize(self.device)
+            pending_error = None
+            try:
+                self.check_status()          # a wait that ran out in the last calls must not vanish with the buffer
+            except RuntimeError as e:
+                pending_error = e
             if self.group is not None and self.size > 1 and self.virtual_peers is None:
                 try:
                     dist.barrier(group=self.group)
@@ -217,6 +301,8 @@ class EPWorld:
             self.control.close()
             self.data = None
             self._ptr_cache.clear()
+            if pending_error is not None:
+                raise pending_error
 
 
 def apply_write(tables: Dict[str, torch.Tensor], name: str, idx: torch.Tensor, val: torch.Tensor) -> None:
@@ -267,6 +353,8 @@ class VirtualCluster:
             kind = kinds.pop()
             if kind == "barrier":
                 sends = [None] * self.n
+                for w in self.worlds:
+                    w.passed_barrier()
             elif kind == "allgather":
                 stacked = torch.stack([r[1] for r in reqs])
                 sends = [stacked] * self.n

@@ -57,12 +57,31 @@ def test_fused_dispatch_gemm_wait_runs_out_and_reports():
         h = buf._drive(eng.layout_gen(idx, E))
         h.topk_weights = w
         h.num_send = torch.zeros_like(h.num_send)          # the dispatch role sends nothing
+        world.set_wait_limit_ms(200)                       # waits on "other ranks" give up after 0.2 s instead of 30 s
         buf._drive(eng.fused_dispatch_gemm_gen(h, x, w, Wg, 0))
         torch.cuda.synchronize()
         st = world.status.tolist()
         assert st[0] in (1, 2) and 600 <= st[1] < 660, st  # a flag or mbarrier wait of the fused kernel
         with pytest.raises(RuntimeError, match="wait ran out"):
             world.check_status()
+        assert world.status.tolist()[0] == 0
+        # with strict status checks the call whose wait ran out is the call that raises
+        world.strict_status = True
+        h2 = buf._drive(eng.layout_gen(idx, E))
+        h2.topk_weights = w
+        h2.num_send = torch.zeros_like(h2.num_send)
+        with pytest.raises(RuntimeError, match="wait ran out"):
+            buf._drive(eng.fused_dispatch_gemm_gen(h2, x, w, Wg, 0))
+        world.strict_status = False
+        assert world.status.tolist()[0] == 0
+        # without them the next call on the buffer raises (the snapshot taken at the end of the failed call)
+        h3 = buf._drive(eng.layout_gen(idx, E))
+        h3.topk_weights = w
+        h3.num_send = torch.zeros_like(h3.num_send)
+        buf._drive(eng.fused_dispatch_gemm_gen(h3, x, w, Wg, 0))
+        with pytest.raises(RuntimeError, match="wait ran out"):
+            buf._drive(eng.layout_gen(idx, E))
+        world.set_wait_limit_ms(0)
         assert world.status.tolist()[0] == 0
         # the context and the buffer are still usable
         saved_mode = engine._FUSED_DISPATCH_MODE

@@ -51,7 +51,7 @@ def test_forward_pair(H, I, counts):
     wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
     row_w = torch.rand(S, device=dev) * valid
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
     act, preact = gemm.fwd_gateup(x, wgu, row_w, me, nmb, status)
     y = gemm.fwd_down(act, wd, me, nmb, status)
     torch.cuda.synchronize()
@@ -77,7 +77,7 @@ def test_backward_pair(H, I, counts):
     wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
     row_w = torch.rand(S, device=dev) * valid
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
     dgu, act_w, parts = gemm.bwd_gradact(dy, wd, preact, row_w, me, nmb, status)
     dx = gemm.bwd_dx(dgu, wgu, me, nmb, status)
     torch.cuda.synchronize()
@@ -101,7 +101,7 @@ def test_wgrad(M, N, counts):
     S, offs, me, nmb, valid = _layout(counts, dev)
     a = (torch.randn(S, M, device=dev) * 0.5).to(torch.bfloat16) * valid[:, None]
     b = (torch.randn(S, N, device=dev) * 0.5).to(torch.bfloat16) * valid[:, None]
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
     dw = gemm.wgrad(a, b, offs, E, status)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0, status.tolist()
@@ -115,6 +115,9 @@ def test_wgrad(M, N, counts):
 @pytest.mark.parametrize("H,I,counts", CASES)
 def test_gather_modes_match_dense(H, I, counts):
     """Row-gather operands (TMA gather4 from a token-once row source) give bitwise the dense results."""
+    from teramoe_b200._build import load_ext
+    if not load_ext().gemm_has_gather4():
+        pytest.skip("the gather4 operand modes are only built with -DTMOE_WITH_GATHER4 (measured too slow for the hot path)")
     dev = "cuda"
     torch.manual_seed(3)
     E = len(counts)
@@ -126,7 +129,7 @@ def test_gather_modes_match_dense(H, I, counts):
     wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
     row_w = torch.rand(S, device=dev) * valid
-    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
     a1, p1 = gemm.fwd_gateup(dense, wgu, row_w, me, nmb, st)
     a2, p2 = gemm.fwd_gateup(rows, wgu, row_w, me, nmb, st, gather_rows=gidx)
     assert torch.equal(a1, a2) and torch.equal(p1, p2)
@@ -157,7 +160,7 @@ def test_cta_pair_kernels_match_one_cta(H, I, counts):
     wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
     wd = (torch.randn(E, H, I, device=dev) * 0.05).to(torch.bfloat16)
     row_w = torch.rand(S, device=dev) * valid
-    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
     a1, p1 = gemm.fwd_gateup(x, wgu, row_w, me, nmb, st)
     a2, p2 = gemm.fwd_gateup(x, wgu, row_w, me, nmb, st, units=units)
     torch.cuda.synchronize()

@@ -5,8 +5,8 @@ PyTorch, code running under a memory pool that forbids raw allocation, a region 
 synchronise the device).  For them the library exports one C function that takes caller-owned
 input and output buffers and keeps its intermediate histograms in a fixed array inside the library.
 This test calls that symbol with ctypes, twice in a row on different inputs (the second smaller,
-so leftovers of the first call would show), and compares with the counts of the regular path.
-It is collected last on purpose.
+so leftovers of the first call would show), and compares with the counts of the regular path and
+with an independent count made by torch.bincount.  It is collected last on purpose.
 """
 import ctypes
 
@@ -28,6 +28,17 @@ def _regular_counts(idx, E, N):
     hist = torch.zeros(chunks * C, dtype=torch.int32, device=idx.device)
     ext.route_hist(idx, E, N, hist)
     return hist.view(chunks, C).sum(0, dtype=torch.int32)
+
+
+def _bincount_counts(idx, E, N):
+    """The same counts from library ops only (no kernel of this repository)."""
+    T, K = idx.shape
+    i = idx.long()
+    valid = (i >= 0) & (i < E)
+    per_expert = torch.bincount(i[valid], minlength=E)
+    dst = torch.where(valid, i // (E // N), torch.full_like(i, N))
+    hit = torch.zeros(T, N + 1, dtype=torch.long, device=idx.device).scatter_(1, dst, 1)[:, :N]
+    return torch.cat([per_expert, hit.sum(0), hit.sum().view(1), torch.tensor([T], device=idx.device)]).to(torch.int32)
 
 
 def test_no_alloc_route_counts_two_calls():
@@ -55,9 +66,13 @@ def test_no_alloc_route_counts_two_calls():
         torch.cuda.synchronize()
         ref = _regular_counts(idx, E, N)
         assert torch.equal(out, ref), (out.tolist()[:8], ref.tolist()[:8])
+        assert torch.equal(out, _bincount_counts(idx, E, N))
         assert out[E + N + 1].item() == T and out[:E].sum().item() == T * K - 1
     # sizes beyond the built-in scratch are refused with a message, nothing is launched
     rc = fn(idx.data_ptr(), 0, 70000, 6, 64, 4, out.data_ptr(), stream, err, 256)
     assert rc == -2 and b"limits" in err.value
     rc = fn(idx.data_ptr(), 0, 100, 6, 4096, 4, out.data_ptr(), stream, err, 256)
     assert rc == -2
+    # a token count near INT_MAX must be refused too (rounding it up to chunks must not wrap around)
+    rc = fn(idx.data_ptr(), 0, 2 ** 31 - 1, 6, 64, 4, out.data_ptr(), stream, err, 256)
+    assert rc == -2 and b"limits" in err.value
