@@ -249,6 +249,7 @@ def main():
             for k, v in rep.items():
                 print(f"  {k:40s} {v:8.3f}", file=sys.stderr)
             print(f"  {'sum':40s} {tot:8.3f}", file=sys.stderr)
+            print("wait times inside the layer kernels (ms per CTA pair):", buf._engine.wait_report(), file=sys.stderr)
 
     def reduce_max(v):
         if world == 1:

@@ -49,6 +49,7 @@ class _TeraMoEFunction(torch.autograd.Function):
         needs_bwd = any(t.requires_grad for t in (x, topk_weights, W_gateup, W_down))
         out, saved = buffer._drive(buffer._engine.forward_gen(x, topk_idx, topk_weights, W_gateup, W_down, num_experts,
                                                               keep_for_backward=needs_bwd, impl=opts))
+        buffer._release()
         ctx.buffer = buffer
         ctx.saved = saved
         ctx.grad_topk_weights = grad_topk_weights
@@ -63,6 +64,7 @@ class _TeraMoEFunction(torch.autograd.Function):
         buffer = ctx.buffer
         dx, gtw, dWgu, dWd = buffer._drive(buffer._engine.backward_gen(ctx.saved, grad_out.contiguous(), W_gateup, W_down,
                                                                       impl=ctx.opts))
+        buffer._release()
         ctx.saved = None
         if ctx.grad_topk_weights is not None:
             ctx.grad_topk_weights.copy_(gtw)
@@ -132,6 +134,11 @@ class Buffer(LowLatencyMixin):
         if self._destroyed:
             raise RuntimeError("Buffer was destroyed")
         return self._world.drive(gen)
+
+    def _release(self) -> None:
+        """Every collective method ends with this, after its last read of the symmetric arena has been enqueued:
+        peers may then overwrite the arena in their next call (EPWorld.release_arena)."""
+        self._world.release_arena()
 
     def check_status(self) -> None:
         """Wait for the kernels enqueued so far and raise if a device-side wait of any of them ran out.  Every call
@@ -302,7 +309,9 @@ class Buffer(LowLatencyMixin):
             if handle is not None:
                 h = handle
                 tabs, _ = self._drive(eng.dispatch_gen(h, x, None, with_meta=False))
-                return tabs["recv_x"][: h.rows].clone(), None, None, None, h
+                got = tabs["recv_x"][: h.rows].clone()
+                self._release()
+                return got, None, None, None, h
             if topk_idx is None or topk_weights is None:
                 raise ValueError("topk_idx and topk_weights are required without a cached handle")
             E = num_experts if num_experts is not None else (int(num_tokens_per_expert.numel()) if num_tokens_per_expert is not None else None)
@@ -313,6 +322,7 @@ class Buffer(LowLatencyMixin):
             tabs, _ = self._drive(eng.dispatch_gen(h, x, topk_weights.float().contiguous(), with_meta=True))
             eng.snapshot_tables(h, tabs)
             recv_x = tabs["recv_x"][: h.rows].clone()
+            self._release()
             R, K = h.rows, h.K
             rs = h.row_slots.long()
             valid = rs >= 0
@@ -350,6 +360,7 @@ class Buffer(LowLatencyMixin):
 
         def run():
             out, cw = self._drive(self._engine.combine_rows_gen(h, x, topk_weights))
+            self._release()
             if bias is not None:
                 for b in (bias if isinstance(bias, (tuple, list)) else (bias,)):
                     if b is not None:
@@ -435,4 +446,5 @@ class Buffer(LowLatencyMixin):
         with torch.no_grad():
             out, _ = self._drive(self._engine.forward_gen(x.contiguous(), topk_idx.contiguous(), topk_weights.float().contiguous(),
                                                           W_gateup, W_down, num_experts, keep_for_backward=False, impl=opts))
+            self._release()
         return out

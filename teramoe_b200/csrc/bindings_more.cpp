@@ -9,6 +9,7 @@
 #include "comm.h"
 #include "fused.h"
 #include "launch_count.h"
+#include "layer.h"
 #include "routing.h"
 #include "runtime.h"
 
@@ -197,11 +198,162 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
     TM_CHECK_CUDA(tmoe::fused_dispatch_gemm((int)kind, bf16(slot_x, "slot_x"), S, bf16(w, "weights"), p, f, (int)num_sms, cur_stream()));
 }
 
+// Whole-layer kernel (layer.cu).
+//   gemm_t : forward  [slot_x view, W_gateup, W_down, act, preact, row_w]
+//            backward [slot_x view, W_down, W_gateup, act_w, dGU, row_w, preact, droute_part, xperm, dW_down, dW_gateup]
+//   layout : [mblock_expert, num_mblocks, unit_blk, num_units, seg_offsets, expert_total_local, unit_order]
+//   send_t : [x, topk_idx, send_order, num_send, send_slot, send_row] (+ [topk_w] in forward)
+//   sym_t  : [arena_ptrs, ctrl_ptrs, blk_cnt view, signal_ptrs, my_signal view]
+//   offs   : [slot_x, slot_w, slot_tk, slot_row, row_first, blk_cnt (control arena), landing, gtw]
+//   push_t : [slot_tk, slot_row, recv_row_base]
+//   red_t  : [landing view, out] (+ [gtw view, gtw_out] in backward)
+//   work_t : [work (int32, 4 per item), num_work, expert_units (int32, 2 per expert), sync (zeroed, 4 + max_units)]
+void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout, std::vector<torch::Tensor> send_t,
+               std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, std::vector<torch::Tensor> push_t,
+               std::vector<torch::Tensor> red_t, std::vector<torch::Tensor> work_t, int64_t E, int64_t N, int64_t rank, int64_t epoch,
+               int64_t num_dispatch_clusters, int64_t group_units, int64_t lag_percent, int64_t min_lag_items, int64_t reduce_chunk,
+               c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<torch::Tensor> stats) {
+    TORCH_CHECK(gemm_t.size() == (bwd ? 11u : 6u) && layout.size() == 7 && send_t.size() == (bwd ? 6u : 7u) && sym_t.size() == 5 &&
+                offs.size() == 8 && push_t.size() == 3 && red_t.size() == (bwd ? 4u : 2u) && work_t.size() == 4,
+                "moe_layer: wrong argument lists");
+    const torch::Tensor& slot_x = gemm_t[0];
+    const int S = (int)slot_x.size(0), H = (int)slot_x.size(1);
+    tmoe::LayerParams p{};
+    p.bwd = bwd ? 1 : 0;
+    p.H = H;
+    p.El = (int)gemm_t[1].size(0);
+    p.I = bwd ? (int)gemm_t[1].size(2) : (int)gemm_t[1].size(1) / 2;
+    p.slot_rows = S;
+    const int R = (int)gemm_t[3].size(0);
+    p.out_rows = R;
+    const TopK tk = topk(send_t[1]);
+    p.T = tk.T; p.K = tk.K; p.E = (int)E; p.N = (int)N; p.rank = (int)rank;
+    p.slot_x = bf16(slot_x, "slot_x");
+    p.w1 = bf16(gemm_t[1], "w1");
+    p.w2 = bf16(gemm_t[2], "w2");
+    p.out0 = bf16(gemm_t[3], "out0");
+    p.out1 = bf16(gemm_t[4], "out1");
+    p.row_w = f32(gemm_t[5], "row_w");
+    TORCH_CHECK(R > 0 && R % 128 == 0 && R <= S && gemm_t[4].size(0) == R && gemm_t[5].numel() >= R, "moe_layer: outputs need a multiple of 128 rows");
+    if (bwd) {
+        p.preact = bf16(gemm_t[6], "preact");
+        p.droute_part = f32(gemm_t[7], "droute_part");
+        p.xperm = bf16(gemm_t[8], "xperm");
+        p.dw_down = bf16(gemm_t[9], "dW_down");
+        p.dw_gateup = bf16(gemm_t[10], "dW_gateup");
+        TORCH_CHECK(gemm_t[6].size(0) >= R && gemm_t[7].size(0) >= R && gemm_t[8].size(0) == R, "moe_layer: backward operands need one row per output row");
+    }
+    check_i32(layout[0], "mblock_expert");
+    p.lay.mblock_expert = layout[0].data_ptr<int>();
+    p.lay.num_mblocks_dev = i32(layout[1], "num_mblocks");
+    p.lay.max_mblocks = R / 128;
+    p.lay.unit_blk = i32(layout[2], "unit_blk");
+    p.lay.num_units_dev = i32(layout[3], "num_units");
+    p.lay.max_units = (int)layout[2].numel() - 1;
+    p.seg_offsets = i32(layout[4], "seg_offsets");
+    p.expert_total_local = i32(layout[5], "expert_total_local");
+    p.unit_order = i32(layout[6], "unit_order");
+    TORCH_CHECK(layout[0].numel() >= R / 128 && layout[6].numel() >= p.lay.max_units && layout[4].numel() == p.El + 1, "moe_layer: layout sizes");
+    p.work = i32(work_t[0], "work");
+    p.max_work = (int)(work_t[0].numel() / 4);
+    p.num_work = i32(work_t[1], "num_work");
+    p.expert_units = i32(work_t[2], "expert_units");
+    p.sync = i32(work_t[3], "sync");
+    TORCH_CHECK(work_t[2].numel() >= 2 * p.El && work_t[3].numel() >= 4 + p.lay.max_units, "moe_layer: work tensors too small");
+    TORCH_CHECK(p.max_work >= tmoe::moe_layer_max_work(p.bwd, p.lay.max_units, H, p.I, p.El, p.T, (int)reduce_chunk), "moe_layer: work list too small");
+    p.group_units = (int)group_units;
+    p.lag_percent = (int)lag_percent;
+    p.min_lag_items = (int)min_lag_items;
+    p.reduce_chunk = (int)reduce_chunk;
+    p.push.arena_ptrs = u64(sym_t[0], "arena_ptrs");
+    p.push.landing_off = (uint64_t)offs[6];
+    p.push.slot_tk = i32(push_t[0], "slot_tk");
+    p.push.slot_row = i32(push_t[1], "slot_row");
+    p.push.recv_row_base = i32(push_t[2], "recv_row_base");
+    p.push.num_ranks = (int)N;
+    TORCH_CHECK(push_t[0].numel() >= R && push_t[1].numel() >= R && push_t[2].numel() == N + 1 && sym_t[0].numel() == N, "moe_layer: push tables");
+    p.gtw_off = bwd ? (uint64_t)offs[7] : 0;
+    p.signal_ptrs = u64(sym_t[3], "signal_ptrs");
+    p.my_signal = i32(sym_t[4], "my_signal");
+    p.epoch = (int)epoch;
+    p.landing = bf16(red_t[0], "landing");
+    p.out = bf16(red_t[1], "out");
+    TORCH_CHECK(red_t[0].size(0) >= (int64_t)tk.T * tk.K && red_t[0].size(1) == H && red_t[1].size(0) == tk.T && red_t[1].size(1) == H, "moe_layer: reduce shapes");
+    if (bwd) {
+        p.gtw_in = f32(red_t[2], "gtw_in");
+        p.gtw_out = f32(red_t[3], "gtw_out");
+        TORCH_CHECK(red_t[2].numel() >= (int64_t)tk.T * tk.K && red_t[3].numel() == (int64_t)tk.T * tk.K, "moe_layer: route gradient shapes");
+    }
+    tmoe::FusedArgs& f = p.f;
+    f.num_dispatch_clusters = (int)num_dispatch_clusters;
+    f.x = bf16(send_t[0], "x");
+    f.topk_idx = tk.ptr;
+    f.idx_is64 = tk.is64;
+    f.send_order = i32(send_t[2], "send_order");
+    f.num_send = i32(send_t[3], "num_send");
+    f.max_send = (int)send_t[2].numel();
+    f.send_slot = i32(send_t[4], "send_slot");
+    f.send_row = i32(send_t[5], "send_row");
+    f.topk_w = bwd ? nullptr : f32(send_t[6], "topk_w");
+    f.T = tk.T; f.K = tk.K; f.H = H; f.E = (int)E; f.N = (int)N;
+    f.with_meta = bwd ? 0 : 1;
+    f.slot_cap = S;
+    f.arena_ptrs = u64(sym_t[0], "arena_ptrs");
+    f.ctrl_ptrs = u64(sym_t[1], "ctrl_ptrs");
+    f.blk_cnt = i32(sym_t[2], "blk_cnt");
+    f.unit_order = p.unit_order;
+    f.seg_offsets = p.seg_offsets;
+    f.expert_total_local = p.expert_total_local;
+    f.off_slot_x = offs[0]; f.off_slot_w = offs[1]; f.off_slot_tk = offs[2]; f.off_slot_row = offs[3]; f.off_row_first = offs[4];
+    f.off_blk_cnt = offs[5];
+    TORCH_CHECK(send_t[0].size(1) == H && send_t[0].size(0) == tk.T && S % 128 == 0 && sym_t[2].numel() >= S / 128, "moe_layer: shape mismatch");
+    TORCH_CHECK(bwd ? (gemm_t[6].size(1) == 2 * p.I) : true, "moe_layer: preact shape");
+    p.status = opt_status(status);
+    p.num_sms = (int)num_sms;
+    if (stats.has_value()) {
+        TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == torch::kInt64 && stats->is_contiguous() && stats->numel() >= tmoe::kLayerStatWords,
+                    "stats must be a contiguous int64 CUDA tensor of 24 words");
+        p.stats = reinterpret_cast<unsigned long long*>(stats->data_ptr<int64_t>());
+    }
+    c10::cuda::CUDAGuard guard(slot_x.device());
+    TM_CHECK_CUDA(tmoe::moe_layer_launch(p, cur_stream()));
+}
+
+// The scheduler kernel of the whole-layer kernel alone (tests read the list back).
+void moe_layer_schedule(bool bwd, int64_t H, int64_t I, int64_t T, torch::Tensor unit_order, torch::Tensor num_units, torch::Tensor seg_offsets,
+                        torch::Tensor unit_blk, torch::Tensor mblock_expert, torch::Tensor expert_total_local, int64_t group_units, int64_t lag_percent, int64_t min_lag_items, int64_t reduce_chunk, torch::Tensor work,
+                        torch::Tensor num_work, torch::Tensor expert_units) {
+    tmoe::LayerParams p{};
+    p.bwd = bwd ? 1 : 0;
+    p.H = (int)H; p.I = (int)I; p.T = (int)T;
+    p.El = (int)seg_offsets.numel() - 1;
+    p.unit_order = i32(unit_order, "unit_order");
+    p.lay.num_units_dev = i32(num_units, "num_units");
+    p.lay.max_units = (int)unit_order.numel();
+    p.seg_offsets = i32(seg_offsets, "seg_offsets");
+    p.lay.unit_blk = i32(unit_blk, "unit_blk");
+    p.lay.mblock_expert = i32(mblock_expert, "mblock_expert");
+    p.expert_total_local = i32(expert_total_local, "expert_total_local");
+    TORCH_CHECK(unit_blk.numel() >= unit_order.numel() + 1 && expert_total_local.numel() == p.El, "moe_layer_schedule: table sizes");
+    p.group_units = (int)group_units; p.lag_percent = (int)lag_percent; p.min_lag_items = (int)min_lag_items; p.reduce_chunk = (int)reduce_chunk;
+    p.work = i32(work, "work");
+    p.max_work = (int)(work.numel() / 4);
+    p.num_work = i32(num_work, "num_work");
+    p.expert_units = i32(expert_units, "expert_units");
+    TORCH_CHECK(expert_units.numel() >= 2 * p.El, "expert_units too small");
+    c10::cuda::CUDAGuard guard(work.device());
+    TM_CHECK_CUDA(tmoe::moe_layer_schedule(p, cur_stream()));
+}
+
+int64_t moe_layer_max_work(bool bwd, int64_t max_units, int64_t H, int64_t I, int64_t El, int64_t T, int64_t reduce_chunk) {
+    return tmoe::moe_layer_max_work(bwd ? 1 : 0, (int)max_units, (int)H, (int)I, (int)El, (int)T, (int)reduce_chunk);
+}
+
 void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site,
-                int64_t limit_ms) {
+                int64_t limit_ms, int64_t mode) {
     c10::cuda::CUDAGuard guard(signal_ptrs.device());
     TM_CHECK_CUDA(tmoe::ep_barrier(u64(signal_ptrs, "signal_ptrs"), (int)rank, (int)N, (int)epoch, opt_status(status), (int)site,
-                                   (int)limit_ms, cur_stream()));
+                                   (int)limit_ms, (int)mode, cur_stream()));
 }
 
 void dispatch_push(torch::Tensor x, torch::Tensor topk_idx, torch::Tensor topk_w, int64_t E, int64_t N, torch::Tensor send_slot,
@@ -313,7 +465,11 @@ void register_more(pybind11::module_& m) {
     m.def("arrival_order", &arrival_order);
     m.def("zero_pad_rows", &zero_pad_rows);
     m.def("fused_dispatch_gemm", &fused_dispatch_gemm);
-    m.def("ep_barrier", &ep_barrier);
+    m.def("moe_layer", &moe_layer);
+    m.def("moe_layer_max_work", &moe_layer_max_work);
+    m.def("moe_layer_schedule", &moe_layer_schedule);
+    m.def("ep_barrier", &ep_barrier, py::arg("signal_ptrs"), py::arg("rank"), py::arg("N"), py::arg("epoch"), py::arg("status"),
+          py::arg("site"), py::arg("limit_ms"), py::arg("mode") = 0);
     m.def("dispatch_push", &dispatch_push);
     m.def("expand_rows", &expand_rows);
     m.def("combine_push", &combine_push);

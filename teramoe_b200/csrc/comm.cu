@@ -26,15 +26,21 @@ namespace tmoe {
 
 namespace {
 
-__global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, uint64_t limit_ns) {
+// mode 0: signal every rank, then wait for every rank (a barrier); 1: signal only; 2: wait only.
+__global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, uint64_t limit_ns,
+                                  int mode) {
     __threadfence_system();
     if ((int)threadIdx.x < N) {
-        int* peer_sig = reinterpret_cast<int*>(signal_ptrs[threadIdx.x]);
-        st_release_sys(peer_sig + rank, epoch);
-        const int* my_sig = reinterpret_cast<const int*>(signal_ptrs[rank]);
-        // A peer that never arrives makes this wait run out: the status block then names the site
-        // (site + peer rank) and the kernel returns normally, so the context stays usable.
-        wait_flag_ge_sys(my_sig + threadIdx.x, epoch, status, site + threadIdx.x, limit_ns);
+        if (mode != 2) {
+            int* peer_sig = reinterpret_cast<int*>(signal_ptrs[threadIdx.x]);
+            st_release_sys(peer_sig + rank, epoch);
+        }
+        if (mode != 1) {
+            const int* my_sig = reinterpret_cast<const int*>(signal_ptrs[rank]);
+            // A peer that never arrives makes this wait run out: the status block then names the site
+            // (site + peer rank) and the kernel returns normally, so the context stays usable.
+            wait_flag_ge_sys(my_sig + threadIdx.x, epoch, status, site + threadIdx.x, limit_ns);
+        }
     }
 }
 
@@ -330,10 +336,10 @@ int grid_for_warps(long warps, int block) {
 
 }  // namespace
 
-cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms,
+cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms, int mode,
                        cudaStream_t stream) {
     const uint64_t limit_ns = limit_ms > 0 ? (uint64_t)limit_ms * 1000000ull : 0ull;   // 0: the status block's run-time limit
-    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns);
+    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns, mode);
     return cudaGetLastError();
 }
 

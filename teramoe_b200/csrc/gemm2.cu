@@ -31,8 +31,6 @@ namespace {
 
 // Pipeline depth: six 32 KB stages; the push epilogue gives one stage up for its staging buffers.
 __host__ __device__ constexpr int stages_for(int epi) { return epi == kEpiPush ? 5 : 6; }
-constexpr int kPushRowBytes = 128 + 16;                        // 64 bf16 columns + pad (bank-conflict-free rows, 16-byte aligned)
-constexpr int kPushWarpBytes = 32 * kPushRowBytes;             // one epilogue warp stages 32 rows x 64 columns
 __host__ __device__ constexpr int smem_bytes_for(int epi) {
     return stages_for(epi) * (16384 + 16384) + 1024 + 256 + (epi == kEpiPush ? kEpiWarps * kPushWarpBytes : 0);
 }
@@ -233,48 +231,9 @@ grouped_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 row = (long)tile.group * g.m_total + m;
             }
             if constexpr (EPI == kEpiPush) {
-                // Combine fused into the GEMM: this warp's 32 rows x 128 columns leave for the ranks that own the
-                // tokens.  Each lane stages its row in shared memory 64 columns (128 bytes) at a time and hands the
-                // segment to a bulk copy shared -> peer global, so no thread of the epilogue waits for NVLink: the
-                // warp goes straight back to draining tensor memory, and only re-using the staging row waits until
-                // the copy engine has READ it (cp.async.bulk.wait_group.read), not until the peer has the bytes.
-                unsigned long long dst_row = 0ull;
-                if (live) {
-                    const int tk = g.slot_tk[row];
-                    if (tk >= 0) {
-                        const int rr = g.slot_row[row];
-                        int src = 0;
-                        while (src + 1 < g.num_ranks && rr >= g.recv_row_base[src + 1]) ++src;
-                        dst_row = g.push_ptrs[src] + g.push_off + (unsigned long long)tk * g.ldd * 2ull;
-                    }
-                }
-                const uint32_t my_stage = push_stage_base + (uint32_t)(warp - 4) * kPushWarpBytes;
-                const uint32_t my_row_smem = my_stage + (uint32_t)lane * kPushRowBytes;
-#pragma unroll 1
-                for (int cg = 0; cg < 2; ++cg) {
-                    tma_store_wait_read<0>();          // this lane's previous segment has left shared memory
-#pragma unroll
-                    for (int c2 = 0; c2 < 2; ++c2) {
-                        uint32_t acc[32];
-                        tmem_ld_x32(taddr0 + (uint32_t)(cg * 64 + c2 * 32), acc);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint32_t p0 = pack_bf16x2(__uint_as_float(acc[8 * v]), __uint_as_float(acc[8 * v + 1]));
-                            const uint32_t p1 = pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
-                            const uint32_t p2 = pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
-                            const uint32_t p3 = pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row_smem + (uint32_t)(c2 * 64 + v * 16)),
-                                         "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
-                        }
-                    }
-                    const int col0 = n0 + cg * 64;
-                    if (dst_row != 0ull && col0 + 64 <= g.n_total) {
-                        fence_proxy_async_smem();      // this lane's generic-proxy stores -> the bulk copy's read
-                        bulk_store_1d(dst_row + (unsigned long long)col0 * 2ull, my_row_smem, 128u);
-                    }
-                    tma_store_commit();
-                }
+                const unsigned long long dst_row = push_row_address(g, row, live, nullptr);
+                const uint32_t my_row_smem = push_stage_base + (uint32_t)(warp - 4) * kPushWarpBytes + (uint32_t)lane * kPushRowBytes;
+                push_epilogue_warp(g, taddr0, dst_row, n0, my_row_smem);
             } else {
                 if (live) epilogue_thread<EPI>(g, taddr0, row_ok ? row : 0, row_ok, n0, tile.n_blk * 2 + h, tile.nk == 0);
             }

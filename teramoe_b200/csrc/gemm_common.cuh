@@ -57,6 +57,11 @@ struct GemmArgs {
     const int* slot_row;                  // [rows] receive row (locates the source rank through recv_row_base)
     const int* recv_row_base;             // [ranks+1]
     int num_ranks;
+    // Backward push (whole-layer kernel only): with gtw_off != 0 the tiles of the first column block also send the
+    // row's route-weight gradient (sum of droute_part[row, :]) to gtw[slot_tk[row]] of the token's rank.
+    unsigned long long gtw_off;
+    const float* droute_in;
+    int n_parts_in;
     const int* gather_rows;      // GATHER modes: source row of each slot-space row (-1 = zero row)
     float* droute_part;          // bwd grad_act: [rows, n_parts]
     int n_parts;
@@ -216,6 +221,60 @@ __device__ __forceinline__ void epilogue_thread(const GemmArgs& g, uint32_t tadd
         }
     }
     if constexpr (EPI == kEpiDSwiGLU) g.droute_part[row * g.n_parts + part_idx] = droute;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Push epilogue (combine fused into the GEMM): an epilogue warp's 32 rows x 128 columns leave for the ranks that
+// own the tokens.  Each lane stages its row in shared memory 64 columns (128 bytes) at a time and hands the segment
+// to a bulk copy shared -> peer global, so no thread of the epilogue waits for NVLink: the warp goes straight back
+// to draining tensor memory, and only re-using the staging row waits until the copy engine has READ it
+// (cp.async.bulk.wait_group.read), not until the peer has the bytes.  The caller ends with tma_store_wait<0>()
+// before the kernel exits or before it tells anyone that the rows are there.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPushRowBytes = 128 + 16;                        // 64 bf16 columns + pad (bank-conflict-free rows, 16-byte aligned)
+constexpr int kPushWarpBytes = 32 * kPushRowBytes;             // one epilogue warp stages 32 rows x 64 columns
+
+// Address of the landing row of output row `row` (0 for pad rows and for rows of a block that is not live).
+__device__ __forceinline__ unsigned long long push_row_address(const GemmArgs& g, long row, bool live, int* src_rank) {
+    if (!live) return 0ull;
+    const int tk = g.slot_tk[row];
+    if (tk < 0) return 0ull;
+    const int rr = g.slot_row[row];
+    int src = 0;
+    while (src + 1 < g.num_ranks && rr >= g.recv_row_base[src + 1]) ++src;
+    if (src_rank != nullptr) *src_rank = src;
+    return g.push_ptrs[src] + g.push_off + (unsigned long long)tk * g.ldd * 2ull;
+}
+
+// taddr0: this warp's tensor-memory lanes and first accumulator column; n0: global column of taddr0;
+// my_row_smem: this lane's staging row (kPushRowBytes apart between lanes).
+__device__ __forceinline__ void push_epilogue_warp(const GemmArgs& g, uint32_t taddr0, unsigned long long dst_row, int n0,
+                                                   uint32_t my_row_smem) {
+#pragma unroll 1
+    for (int cg = 0; cg < 2; ++cg) {
+        tma_store_wait_read<0>();          // this lane's previous segment has left shared memory
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t acc[32];
+            tmem_ld_x32(taddr0 + (uint32_t)(cg * 64 + c2 * 32), acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint32_t p0 = pack_bf16x2(__uint_as_float(acc[8 * v]), __uint_as_float(acc[8 * v + 1]));
+                const uint32_t p1 = pack_bf16x2(__uint_as_float(acc[8 * v + 2]), __uint_as_float(acc[8 * v + 3]));
+                const uint32_t p2 = pack_bf16x2(__uint_as_float(acc[8 * v + 4]), __uint_as_float(acc[8 * v + 5]));
+                const uint32_t p3 = pack_bf16x2(__uint_as_float(acc[8 * v + 6]), __uint_as_float(acc[8 * v + 7]));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row_smem + (uint32_t)(c2 * 64 + v * 16)),
+                             "r"(p0), "r"(p1), "r"(p2), "r"(p3) : "memory");
+            }
+        }
+        const int col0 = n0 + cg * 64;
+        if (dst_row != 0ull && col0 + 64 <= g.n_total) {
+            fence_proxy_async_smem();      // this lane's generic-proxy stores -> the bulk copy's read
+            bulk_store_1d(dst_row + (unsigned long long)col0 * 2ull, my_row_smem, 128u);
+        }
+        tma_store_commit();
+    }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -260,6 +260,17 @@ __device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_add
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+// Hand 16 bytes to the other CTA of the pair without any fence: the store travels through the async proxy and counts
+// 16 bytes on an mbarrier of the destination CTA (like a TMA load does), so a plain wait on that barrier is enough to
+// see the data.  `addr` and `bar` are shared::cluster addresses in the same destination CTA.  The barrier also needs one
+// arrival that expects the 16 bytes (mbar_arrive_expect_tx_cluster, from this CTA, in either order).
+__device__ __forceinline__ void st_async_v4_cluster(uint32_t addr, int4 v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster_acquire(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

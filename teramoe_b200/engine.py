@@ -96,6 +96,17 @@ def dispatch_pairs(kind: int, num_dispatch_sms: int = 0) -> int:
 FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4"))
 
 
+# The whole layer direction as ONE cooperative kernel (csrc/layer.cu): dispatch, both GEMMs, the combine push, the
+# weight gradients (backward) and the reduce run as items of one work list.  "auto": wherever the fused dispatch applies.
+_LAYER_KERNEL_MODE = os.environ.get("TERAMOE_LAYER_KERNEL", "auto")
+LAYER_REDUCE_CHUNK = 64          # tokens per reduce item
+LAYER_MIN_LAG_PER_PAIR = float(os.environ.get("TERAMOE_LAYER_MIN_LAG", "2"))
+
+
+def use_layer_kernel() -> bool:
+    return _LAYER_KERNEL_MODE != "0"
+
+
 def use_fused_dispatch(I: int, num_ranks: int, table_bytes: int = 0) -> bool:
     if not USE_CTA_PAIRS or USE_TMA_GATHER:
         return False
@@ -130,6 +141,8 @@ class LayerHandle:
     num_send: Optional[torch.Tensor] = None      # device scalar: number of entries in send_order
     unit_order: Optional[torch.Tensor] = None    # fused dispatch: units sorted by arrival group
     fused_dispatch: bool = False
+    layer_kernel: bool = False                   # the whole direction runs as one kernel (csrc/layer.cu)
+    opts: Optional[dict] = None                  # schedule knobs of the layer call (compute_batch_size, ...)
     num_dispatch_sms: int = 0                    # SMs that dispatch first in the fused dispatch + GEMM kernel (0: default)
     unit_blk: Optional[torch.Tensor] = None      # CTA-pair GEMMs: first block of every unit (+ sentinel)
     num_units: Optional[torch.Tensor] = None
@@ -179,6 +192,8 @@ class EPEngine:
         self.is_cuda = world.is_cuda
         self.ext = world.ext if self.is_cuda else None
         self._trace = None          # list of (phase name, CUDA event) while tracing
+        self.last_wait_ns = {}      # whole-layer kernel: {0: forward, 1: backward} -> int64[8] wait counters (csrc/layer.h LayerStat)
+        self.last_paths = {}
 
     # ------------------------------------------------------------------ phase tracing
     def enable_trace(self, on: bool = True) -> None:
@@ -214,27 +229,11 @@ class EPEngine:
         return {k: acc[k] / cnt[k] for k in acc}
 
     # ------------------------------------------------------------------ arena reuse between calls
-    # Peers store into this rank's arena; the arena is reused by every call.  What makes that safe:
-    #  (1) every read of a table in a call is stream-ordered before the call's last barrier signal, except the reads
-    #      registered with `_late` (the reduce of the landed rows, the clones of an un-fused dispatch);
-    #  (2) a peer writes a table in its NEXT call either after a barrier of that call (forward: the count exchange), or
-    #      rows that this rank asked for in that same call (combine pushes answer this rank's own dispatch, which it
-    #      issued after its late reads), or, for the remaining case, pushes without a barrier first (backward
-    #      dispatch, cached-handle dispatch, un-fused combine), after `_entry_barrier` found no overlap between what is
-    #      about to be written and the registered late reads (same layer, same geometry: disjoint tables) or crossed
-    #      one more barrier.
-    def _ranges(self, h: LayerHandle, H: int, offs, names):
-        sizes, _ = _table_sizes(h.maxima, H, h.K)
-        return [(offs[n], sizes[n]) for n in names if n in offs]
-
-    def _late(self, h: LayerHandle, H: int, offs, names) -> None:
-        if self.is_cuda:
-            for off, n in self._ranges(h, H, offs, names):
-                self.world.note_late_read(off, n)
-
-    def _entry_barrier(self, h: LayerHandle, H: int, offs, names):
-        if self.is_cuda and self.world.size > 1 and self.world.needs_entry_barrier(self._ranges(h, H, offs, names)):
-            yield ("barrier",)
+    def _acquire(self):
+        """Before pushes that no barrier of the same call precedes: wait until every rank has released the arena after
+        its previous call (EPWorld.release_arena / acquire_arena)."""
+        if self.is_cuda and self.world.size > 1:
+            yield ("acquire",)
 
     # ------------------------------------------------------------------ table access
     def _tables(self, offs, maxima, H, K, dtype):
@@ -337,8 +336,8 @@ class EPEngine:
         if self.is_cuda:
             yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, x.dtype)
-        pushed = ("recv_x",) + (("slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots") if with_meta else ())
-        yield from self._entry_barrier(h, H, offs, pushed)
+        if not with_meta:      # cached handle / backward: no barrier of this call precedes the pushes
+            yield from self._acquire()
         if self.is_cuda:
             ext = self.ext
             if with_meta:
@@ -358,7 +357,6 @@ class EPEngine:
         self._mark("  dispatch push kernel")
         yield ("barrier",)
         self._mark("  dispatch barrier")
-        self._late(h, H, offs, pushed)        # the caller reads (clones, expands) these after the barrier
         return tabs, offs
 
     def snapshot_tables(self, h: LayerHandle, tabs) -> None:
@@ -416,14 +414,12 @@ class EPEngine:
     def combine_gen(self, h: LayerHandle, y: torch.Tensor, tabs, offs, droute_parts: Optional[torch.Tensor] = None):
         """Sum each received token's local expert outputs and push one row back to its source; after
         the barrier reduce the landed rows.  -> (out [T,H], gtw [T,K] or None)."""
-        yield from self._entry_barrier(h, h.H, offs, ("landing", "gtw"))
         writes = self._combine_push(h, y, offs, droute_parts)
         if writes is not None:
             yield ("push", writes)
         self._mark("  combine push kernel")
         yield ("barrier",)
         self._mark("  combine barrier")
-        self._late(h, h.H, offs, ("landing", "gtw"))
         res = self._combine_reduce(h, tabs, y.dtype, y.device, droute_parts is not None)
         self._mark("  combine reduce kernel")
         return res
@@ -448,7 +444,7 @@ class EPEngine:
         hh.row_slots = torch.full((R, K), -1, dtype=torch.int32, device=dev)
         if R:
             hh.row_slots[:, 0] = torch.arange(R, dtype=torch.int32, device=dev)
-        yield from self._entry_barrier(hh, hh.H, offs, ("landing", "gtw"))
+        yield from self._acquire()
         writes = [self._combine_push(hh, x.contiguous(), offs, None)]
         if recv_topk_weights is not None:
             # the side channel is indexed by slot: scatter the received weights into slot space
@@ -463,7 +459,6 @@ class EPEngine:
             if wri is not None:
                 yield ("push", wri)
         yield ("barrier",)
-        self._late(hh, hh.H, offs, ("landing", "gtw"))
         return self._combine_reduce(hh, tabs, x.dtype, dev, recv_topk_weights is not None)
 
     def slots_combine_gen(self, h: LayerHandle, y: torch.Tensor, weights: Optional[torch.Tensor]):
@@ -476,7 +471,7 @@ class EPEngine:
         if self.is_cuda:
             yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, y.dtype)
-        yield from self._entry_barrier(h, H, offs, ("landing",))
+        yield from self._acquire()
         if self.is_cuda:
             if h.slots > 0:
                 self.ext.slot_rows_push(y.contiguous(), h.slot_tk, h.slot_row, h.recv_row_base, h.slots, w.ptr_table(w.data, 0, "data"),
@@ -491,7 +486,6 @@ class EPEngine:
                 writes[s] = [("landing", h.slot_tk.long()[valid[m]], y[valid[m]])]
             yield ("push", writes)
         yield ("barrier",)
-        self._late(h, H, offs, ("landing",))
         out = torch.empty(T, H, dtype=y.dtype, device=y.device)
         if T == 0:
             return out
@@ -532,6 +526,14 @@ class EPEngine:
         self.last_paths = {"fused_dispatch_gemm": h.fused_dispatch, "cta_pairs": bool(units is not None),
                            "fused_combine_fwd": bool(self.is_cuda and use_fused_combine(I, w.size, False)),
                            "fused_combine_bwd": bool(self.is_cuda and use_fused_combine(I, w.size, True))}
+        h.layer_kernel = bool(h.fused_dispatch and use_layer_kernel())
+        self.last_paths["layer_kernel"] = h.layer_kernel
+        if h.layer_kernel:
+            h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
+            h.opts = dict(impl or {})
+            out, preact, saved_x = yield from self.layer_kernel_gen(h, 0, x, topk_weights, W_gateup, W_down, num_sms=num_sms)
+            saved = SavedForBackward(h, saved_x, preact, stats=self._stats(h, H)) if keep_for_backward else None
+            return out, saved
         if h.fused_dispatch:
             h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
             tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms,
@@ -565,7 +567,6 @@ class EPEngine:
             self._mark("fwd:down GEMM + pushed combine")
             yield ("barrier",)
             self._mark("fwd:combine barrier")
-            self._late(h, H, offs, ("landing",))
             out = torch.empty(T, H, dtype=x.dtype, device=x.device)
             if T > 0:
                 self.ext.combine_reduce_slots(tabs["landing"], h.topk_idx, h.E, out, None)
@@ -577,8 +578,38 @@ class EPEngine:
             out, _ = yield from self.combine_gen(h, y, tabs, offs)
             del y
         self._mark("fwd:combine (rest)")
-        saved = SavedForBackward(h, saved_x, preact) if keep_for_backward else None
+        saved = SavedForBackward(h, saved_x, preact, stats=self._stats(h, H)) if keep_for_backward else None
         return out, saved
+
+    def wait_report(self) -> dict:
+        """Wait times of the last whole-layer kernels in ms per CTA pair (mean): how long the producers waited for
+        rows of other ranks, for the first GEMM of a unit, for an expert's units (weight gradients), and how long the
+        gather waited for every rank's pushes."""
+        names = ("wait_arrival", "wait_first_gemm", "wait_wgrad", "wait_landed")
+        rep = {}
+        pairs = max(1, torch.cuda.get_device_properties(self.world.device).multi_processor_count // 2) if self.is_cuda else 1
+        for kind, t in self.last_wait_ns.items():
+            v = t.tolist()
+            d = {n: round(v[i] / 1e6 / (pairs if i < 3 else pairs * 2), 4) for i, n in enumerate(names)}
+            # when the epilogues took the first / finished the last item of every kind, relative to the first item at all
+            firsts = {k: ~v[8 + k] & 0xFFFFFFFFFFFFFFFF for k in range(5) if v[8 + k] != 0}
+            if firsts:
+                t0 = min(firsts.values())
+                kinds = ("gemm1", "gemm2", "wgrad_down", "wgrad_gateup", "reduce")
+                d["spans_ms"] = {kinds[k]: (round((firsts[k] - t0) / 1e6, 3), round(((v[16 + k] & 0xFFFFFFFFFFFFFFFF) - t0) / 1e6, 3)) for k in firsts}
+            rep["bwd" if kind else "fwd"] = d
+        return rep
+
+    def _stats(self, h: LayerHandle, H: int) -> dict:
+        """Per-call numbers of the layer (tokens received, rows per expert, bytes that crossed NVLink)."""
+        K, N = h.K, h.N
+        fused = h.fused_dispatch
+        return {"tokens": h.T, "rows_received": h.rows, "slots": h.slots, "per_expert_rows": h.expert_total_local,
+                "paths": dict(self.last_paths),
+                # bytes this rank RECEIVES per transfer: the fused paths move one row per (token, k) entry, the separate
+                # kernels one row per (token, rank)
+                "dispatch_bytes": (int(h.slots) if fused else int(h.rows)) * H * 2,
+                "combine_bytes": (h.T * K if fused else int(h.land_rows)) * H * 2}
 
     def _grid_sms(self, impl) -> int:
         """`total_sms` of the layer call limits the grids of the GEMM kernels (0: all SMs of the device)."""
@@ -601,7 +632,8 @@ class EPEngine:
         offs, total, maxima = _arena_geometry(h.maxima, H, K, True)
         yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, rows_in.dtype)
-        yield from self._entry_barrier(h, H, offs, ("slot_x", "slot_w", "slot_tk", "slot_row", "row_first"))
+        if kind == 1:
+            yield from self._acquire()
         S = h.slots
         dev = rows_in.device
         if kind == 0:
@@ -633,6 +665,95 @@ class EPEngine:
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         return tabs, offs, out0, out1, parts
 
+    def layer_kernel_gen(self, h: LayerHandle, kind: int, rows_in, topk_weights, w1, w2, saved: Optional[SavedForBackward] = None,
+                         num_sms=0):
+        """One direction of the layer as ONE cooperative kernel (csrc/layer.cu) behind the routing preparation.
+        kind 0: rows_in = x, w1 = W_gateup, w2 = W_down -> (out [T,H], preact, saved_x).
+        kind 1: rows_in = grad_out, w1 = W_down, w2 = W_gateup -> (dx, d(topk_weights), dW_gateup, dW_down)."""
+        w, ext = self.world, self.ext
+        T, H = rows_in.shape
+        K, N, E = h.K, h.N, h.E
+        h.H = H
+        bwd = kind == 1
+        I = w1.shape[2] if bwd else w1.shape[1] // 2
+        El = w1.shape[0]
+        dev = rows_in.device
+        opts = h.opts or {}
+        offs, total, maxima = _arena_geometry(h.maxima, H, K, True)
+        yield ("grow", total)
+        tabs = self._tables(offs, maxima, H, K, rows_in.dtype)
+        S = h.slots
+        R = max(S, 128)                                      # rows of the tensors of this call (the kernel wants >= one block)
+        i32 = dict(dtype=torch.int32, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        if bwd:
+            xperm = torch.empty(R, H, **bf)
+            if S > 0:
+                ext.expand_rows(saved.saved_x, h.slot_row, xperm, S)          # X back in slot space: operand of dW_gateup
+            self._mark("bwd:expand X")
+            yield from self._acquire()                       # no barrier of this call precedes the pushes
+        else:
+            ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert,
+                              h.unit_blk, h.num_units)
+            h.unit_order = torch.zeros(h.unit_blk.numel(), **i32)
+            blk_group = torch.zeros(max(S // 128, 1), **i32)
+            ext.arrival_order(w.meta_view(E + N + 2), h.rank, N, E, max(1, min(FUSED_DISPATCH_GROUPS, N)), h.seg_offsets, h.unit_blk,
+                              h.num_units, blk_group, h.unit_order)
+        ext.zero_pad_rows(h.seg_offsets, h.expert_total_local, tabs["slot_x"])
+        out0 = torch.empty(R, I, **bf)
+        out1 = torch.empty(R, 2 * I, **bf)
+        out = torch.empty(T, H, **bf)
+        max_units = h.unit_blk.numel() - 1
+        max_work = ext.moe_layer_max_work(bwd, max_units, H, I, El, T, LAYER_REDUCE_CHUNK)
+        work_t = [torch.empty(max_work * 4, **i32), torch.empty(1, **i32), torch.empty(2 * El, **i32), torch.zeros(4 + max_units, **i32)]
+        layout = [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units, h.seg_offsets, h.expert_total_local, h.unit_order]
+        send_t = [rows_in, h.topk_idx, h.send_order, h.num_send, h.send_slot.view(-1), h.send_row]
+        if bwd:
+            parts = torch.empty(R, gemm.num_droute_parts(I), dtype=torch.float32, device=dev)
+            dW_down = torch.empty(El, H, I, **bf)
+            dW_gateup = torch.empty(El, 2 * I, H, **bf)
+            gtw_out = torch.empty(T, K, dtype=torch.float32, device=dev)
+            gemm_t = [tabs["slot_x"], w1, w2, out0, out1, h.slot_w if S > 0 else torch.zeros(R, device=dev), saved.preact, parts, xperm,
+                      dW_down, dW_gateup]
+            if saved.preact.shape[0] < R:
+                gemm_t[6] = torch.zeros(R, 2 * I, **bf)
+            push_t = [h.slot_tk, h.slot_row, h.recv_row_base] if S > 0 else [torch.full((R,), -1, **i32), torch.full((R,), -1, **i32),
+                                                                             h.recv_row_base]
+            red_t = [tabs["landing"], out, tabs["gtw"], gtw_out]
+        else:
+            send_t.append(topk_weights)
+            gemm_t = [tabs["slot_x"], w1, w2, out0, out1, tabs["slot_w"]]
+            push_t = [tabs["slot_tk"], tabs["slot_row"], h.recv_row_base]
+            red_t = [tabs["landing"], out]
+        sym_t = [w.ptr_table(w.data, 0, "data"), w.ptr_table(w.control, 0, "control_base"), w.blk_cnt_view(),
+                 w.ptr_table(w.control, w.signal_offset, "control_sig"), w.control.view(w.signal_offset, [N], torch.int32)]
+        offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset,
+                   offs["landing"], offs["gtw"]]
+        group_units = max(1, int(opts.get("compute_batch_size", 2048)) // 256)
+        lag = int(opts.get("combine_start_head_percent", 70))
+        # a second-GEMM item should find its unit's first GEMM finished, not merely claimed: keep it about two items per
+        # CTA pair behind (TERAMOE_LAYER_MIN_LAG: items per pair)
+        sms = num_sms or torch.cuda.get_device_properties(dev).multi_processor_count
+        min_lag = int(LAYER_MIN_LAG_PER_PAIR * (sms // 2))
+        # per-role wait times of this launch (ns summed over waiting threads), kept on the device until somebody asks
+        wait_ns = torch.zeros(24, dtype=torch.int64, device=dev)
+        self.last_wait_ns[kind] = wait_ns
+        ext.moe_layer(bwd, gemm_t, layout, send_t, sym_t, offsets, push_t, red_t, work_t, E, N, h.rank, w.next_epoch(),
+                      dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns)
+        # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
+        w.blk_cnt_view()[: max(S // 128, 1)].zero_()
+        if bwd:
+            self._mark("bwd:layer kernel (dispatch, grad_act, dX + combine, weight gradients, reduce)")
+            return out, gtw_out, dW_gateup, dW_down
+        self._mark("fwd:layer kernel (dispatch, gate_up, down + combine, reduce)")
+        R_rows = h.rows
+        h.slot_row, h.slot_w, h.slot_tk = tabs["slot_row"][:S].clone(), tabs["slot_w"][:S].clone(), tabs["slot_tk"][:S].clone()
+        saved_x = torch.empty(R_rows, H, **bf)
+        if R_rows > 0:
+            ext.expand_rows(tabs["slot_x"], tabs["row_first"], saved_x, R_rows)     # one slot per received token
+        self._mark("fwd:save tables and X")
+        return out, out1[:S] if S < R else out1, saved_x
+
     def _push_target(self, h: LayerHandle, offs):
         w = self.world
         return ([w.ptr_table(w.data, 0, "data"), h.slot_tk, h.slot_row, h.recv_row_base], offs["landing"])
@@ -644,6 +765,8 @@ class EPEngine:
         st = w.status if self.is_cuda else None
         num_sms = num_sms or self._grid_sms(impl)
         self._mark("bwd:start")
+        if h.layer_kernel:
+            return (yield from self.layer_kernel_gen(h, 1, grad_out, None, W_down, W_gateup, saved=saved, num_sms=num_sms))
         if h.fused_dispatch:
             tabs, offs, act_w, dgu, parts = yield from self.fused_dispatch_gemm_gen(h, grad_out, None, W_down, 1, preact=saved.preact,
                                                                                     num_sms=num_sms, num_dispatch_sms=h.num_dispatch_sms)
@@ -726,7 +849,6 @@ class EPEngine:
             # weight gradients were enqueued after the push so they overlap the other ranks' pushes
             yield ("barrier",)
             self._mark("bwd:combine barrier")
-            self._late(h, h.H, offs, ("landing", "gtw"))
             T, K = h.T, h.K
             dx = torch.empty(T, h.H, dtype=grad_out.dtype, device=grad_out.device)
             if T > 0:

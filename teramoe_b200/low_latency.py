@@ -149,6 +149,7 @@ class LowLatencyMixin:
             tabs, _ = self._drive(eng.dispatch_gen(h, x.contiguous(), ones, with_meta=True))
             eng.snapshot_tables(h, tabs)
             rows = tabs["recv_x"][: h.rows].clone()
+            self._release()
             xperm = eng.expand(rows, h)
             counts = h.expert_total_local.to(torch.int32)
             if int(counts.max()) > N * M if counts.numel() else False:
@@ -202,6 +203,7 @@ class LowLatencyMixin:
                 payload = logfmt10_roundtrip(payload)
             y[handle.slot_ids] = payload
             res = self._drive(eng.slots_combine_gen(h, y, topk_weights.float().contiguous()))
+            self._release()
             if out is not None:
                 out.copy_(res)
                 return out

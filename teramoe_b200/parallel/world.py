@@ -13,6 +13,7 @@ Three ways to run the same per-rank pipeline (teramoe_b200/engine.py):
 
 The pipeline is written as a generator that yields where it needs something from other ranks:
   ("barrier",)            all ranks reached this point and their peer stores are visible
+  ("acquire",)            every rank has released the data arena after its previous call (see release_arena)
   ("allgather", tensor)   -> stacked tensor of all ranks (host path only)
   ("grow", nbytes)        the data arena must hold nbytes on every rank (all ranks ask together)
   ("push", {dst: [...]})  host path only: writes into peers' tables
@@ -54,7 +55,8 @@ class EPWorld:
         if self.is_cuda:
             from .._build import load_ext
             self.ext = load_ext()
-            self.signal_offset = size * CONTROL_ROW_INTS * 4
+            self.signal_offset = size * CONTROL_ROW_INTS * 4      # barrier / push-complete flags, one int per rank
+            self.free_offset = self.signal_offset + 512           # arena-release flags, one int per rank
             self.blk_cnt_offset = self.signal_offset + 1024
             self.control_bytes = _round_up(self.blk_cnt_offset + MAX_BLOCKS * 4 + 4096)
             with torch.cuda.device(self.device):
@@ -69,8 +71,7 @@ class EPWorld:
             if ms > 0:
                 self.set_wait_limit_ms(ms)
         self.strict_status = STRICT_STATUS
-        # byte ranges of the data arena that the previous call still reads after its last barrier
-        self._late_reads: List[tuple] = []
+        self._release_seq = 0            # calls whose arena reads this rank has released (same on all ranks at the same call)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -200,24 +201,25 @@ class EPWorld:
                 self._raise_status(self._status_ring[row].tolist())
 
     # ------------------------------------------------------------------ arena reuse between calls
-    def note_late_read(self, offset: int, nbytes: int) -> None:
-        """The current call reads [offset, offset+nbytes) of the data arena AFTER its last barrier."""
-        if nbytes > 0:
-            self._late_reads.append((int(offset), int(offset) + int(nbytes)))
+    # Peers store into this rank's data arena and every call reuses it.  The rule that makes this safe: a rank
+    # RELEASES its arena when it has enqueued the last read of a call (a signal-only kernel: one flag per peer, no
+    # wait), and a call that lets peers write without having crossed a barrier first (backward dispatch, cached-handle
+    # dispatch, un-fused combine) first ACQUIRES: it waits (a wait-only kernel on local flags, normally satisfied
+    # long ago) until every rank has released as many calls as this rank has.  A forward needs no acquire: its count
+    # exchange is a barrier that every rank signals after its previous call.  Combine pushes need none either: a peer
+    # only pushes rows that this rank asked for in the same call.
+    def release_arena(self) -> None:
+        if not self.is_cuda or self.size == 1 or self.virtual_peers is not None:
+            return
+        self._release_seq += 1
+        self.ext.ep_barrier(self.ptr_table(self.control, self.free_offset, "control_free"), self.rank, self.size, self._release_seq,
+                            self.status, 540, 0, 1)
 
-    def passed_barrier(self) -> None:
-        self._late_reads.clear()
-
-    def needs_entry_barrier(self, write_ranges) -> bool:
-        """A call is about to let peers write `write_ranges` [(offset, nbytes)] of this rank's arena without having
-        crossed a barrier first.  That is safe only if no rank can still be reading those bytes from the previous call:
-        every read of a call is ordered before the call's last barrier signal except the ones registered with
-        note_late_read.  All ranks run the same calls with the same geometry, so they all answer the same."""
-        for off, n in write_ranges:
-            for lo, hi in self._late_reads:
-                if off < hi and lo < off + n:
-                    return True
-        return False
+    def acquire_arena(self) -> None:
+        if not self.is_cuda or self.size == 1 or self.virtual_peers is not None or self._release_seq == 0:
+            return
+        self.ext.ep_barrier(self.ptr_table(self.control, self.free_offset, "control_free"), self.rank, self.size, self._release_seq,
+                            self.status, 560, 0, 2)
 
     def device_barrier(self, site: int = 500, limit_ms: int = 0) -> None:
         """Bounded all-rank barrier kernel on the current stream (limit_ms <= 0: the default 2 s)."""
@@ -240,7 +242,9 @@ class EPWorld:
                         self.device_barrier()
                     else:
                         self._cpu_exchange_pushes()
-                    self.passed_barrier()
+                    req = gen.send(None)
+                elif kind == "acquire":
+                    self.acquire_arena()
                     req = gen.send(None)
                 elif kind == "allgather":
                     t = req[1]
@@ -351,10 +355,8 @@ class VirtualCluster:
             kinds = {r[0] for r, d in zip(reqs, done) if not d}
             assert len(kinds) == 1 and not any(done), f"ranks diverged: {kinds}"
             kind = kinds.pop()
-            if kind == "barrier":
+            if kind in ("barrier", "acquire"):      # ranks of a virtual cluster run one after the other on one stream
                 sends = [None] * self.n
-                for w in self.worlds:
-                    w.passed_barrier()
             elif kind == "allgather":
                 stacked = torch.stack([r[1] for r in reqs])
                 sends = [stacked] * self.n
