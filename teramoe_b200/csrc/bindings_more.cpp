@@ -70,6 +70,7 @@ tmoe::LayoutOut layout_out(const std::vector<torch::Tensor>& t) {
     o.sizes = i32(t[7], "sizes");
     o.send_base = i32(t[8], "send_base");
     TORCH_CHECK(t[6].numel() >= 2, "num_mblocks must hold 2 ints");
+    TORCH_CHECK(t[7].numel() >= 12, "sizes must hold 12 ints");
     return o;
 }
 
@@ -95,20 +96,23 @@ void route_scan(torch::Tensor chunk_hist, torch::Tensor chunk_base, int64_t num_
                                    cur_stream()));
 }
 
-void layout_finalize(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, std::vector<torch::Tensor> layout) {
+void layout_finalize(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, std::vector<torch::Tensor> layout, int64_t cap_rows,
+                     int64_t cap_slots, int64_t cap_tokens) {
     c10::cuda::CUDAGuard guard(meta.device());
-    TM_CHECK_CUDA(tmoe::layout_finalize(i32(meta, "meta"), (int)rank, (int)N, (int)E, layout_out(layout), cur_stream()));
+    TM_CHECK_CUDA(tmoe::layout_finalize(i32(meta, "meta"), (int)rank, (int)N, (int)E, layout_out(layout), (int)cap_rows, (int)cap_slots,
+                                        (int)cap_tokens, cur_stream()));
 }
 
 void slot_pad_fill(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_row, torch::Tensor slot_w,
                    torch::Tensor slot_tk, torch::Tensor mblock_expert, c10::optional<torch::Tensor> unit_blk,
-                   c10::optional<torch::Tensor> num_units) {
+                   c10::optional<torch::Tensor> num_units, c10::optional<torch::Tensor> ok) {
     c10::cuda::CUDAGuard guard(seg_offsets.device());
     TM_CHECK_CUDA(tmoe::slot_pad_fill(i32(seg_offsets, "seg_offsets"), i32(expert_total_local, "expert_total_local"),
                                       (int)expert_total_local.numel(), i32(slot_row, "slot_row"), f32(slot_w, "slot_w"),
                                       i32(slot_tk, "slot_tk"), i32(mblock_expert, "mblock_expert"),
                                       unit_blk.has_value() ? i32(*unit_blk, "unit_blk") : nullptr,
-                                      num_units.has_value() ? i32(*num_units, "num_units") : nullptr, cur_stream()));
+                                      num_units.has_value() ? i32(*num_units, "num_units") : nullptr,
+                                      ok.has_value() ? i32(*ok, "ok") : nullptr, cur_stream()));
 }
 
 void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_base, std::vector<torch::Tensor> layout,
@@ -122,17 +126,19 @@ void route_assign(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor ch
 }
 
 void arrival_order(torch::Tensor meta, int64_t rank, int64_t N, int64_t E, int64_t groups, torch::Tensor seg_offsets, torch::Tensor unit_blk,
-                   torch::Tensor num_units, torch::Tensor blk_group, torch::Tensor unit_order) {
+                   torch::Tensor num_units, torch::Tensor blk_group, torch::Tensor unit_order, c10::optional<torch::Tensor> ok) {
     c10::cuda::CUDAGuard guard(meta.device());
     TM_CHECK_CUDA(tmoe::arrival_order(i32(meta, "meta"), (int)rank, (int)N, (int)E, (int)groups, i32(seg_offsets, "seg_offsets"),
                                       i32(unit_blk, "unit_blk"), i32(num_units, "num_units"), (int)unit_blk.numel() - 1,
-                                      i32(blk_group, "blk_group"), i32(unit_order, "unit_order"), cur_stream()));
+                                      i32(blk_group, "blk_group"), i32(unit_order, "unit_order"), ok.has_value() ? i32(*ok, "ok") : nullptr,
+                                      cur_stream()));
 }
 
-void zero_pad_rows(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_x) {
+void zero_pad_rows(torch::Tensor seg_offsets, torch::Tensor expert_total_local, torch::Tensor slot_x, c10::optional<torch::Tensor> ok) {
     c10::cuda::CUDAGuard guard(slot_x.device());
     TM_CHECK_CUDA(tmoe::zero_pad_rows(i32(seg_offsets, "seg_offsets"), i32(expert_total_local, "expert_total_local"),
-                                      (int)expert_total_local.numel(), bf16(slot_x, "slot_x"), (int)slot_x.size(1), cur_stream()));
+                                      (int)expert_total_local.numel(), bf16(slot_x, "slot_x"), (int)slot_x.size(1),
+                                      ok.has_value() ? i32(*ok, "ok") : nullptr, cur_stream()));
 }
 
 // Fused dispatch + GEMM.  kind 0 forward (gate_up + SwiGLU), 1 backward (grad_act + dSwiGLU).
@@ -207,12 +213,13 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
 //   offs   : [slot_x, slot_w, slot_tk, slot_row, row_first, blk_cnt (control arena), landing, gtw]
 //   push_t : [slot_tk, slot_row, recv_row_base]
 //   red_t  : [landing view, out] (+ [gtw view, gtw_out] in backward)
-//   work_t : [work (int32, 4 per item), num_work, expert_units (int32, 2 per expert), sync (zeroed, 4 + max_units)]
+//   work_t : [work (int32, 4 per item), num_work, expert_units (int32, 2 per expert), sync (zeroed, 8 + max_units)]
 void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout, std::vector<torch::Tensor> send_t,
                std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, std::vector<torch::Tensor> push_t,
                std::vector<torch::Tensor> red_t, std::vector<torch::Tensor> work_t, int64_t E, int64_t N, int64_t rank, int64_t epoch,
                int64_t num_dispatch_clusters, int64_t group_units, int64_t lag_percent, int64_t min_lag_items, int64_t reduce_chunk,
-               c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<torch::Tensor> stats) {
+               c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<torch::Tensor> stats,
+               c10::optional<torch::Tensor> x_rows, c10::optional<torch::Tensor> ok) {
     TORCH_CHECK(gemm_t.size() == (bwd ? 11u : 6u) && layout.size() == 7 && send_t.size() == (bwd ? 6u : 7u) && sym_t.size() == 5 &&
                 offs.size() == 8 && push_t.size() == 3 && red_t.size() == (bwd ? 4u : 2u) && work_t.size() == 4,
                 "moe_layer: wrong argument lists");
@@ -259,7 +266,7 @@ void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::T
     p.num_work = i32(work_t[1], "num_work");
     p.expert_units = i32(work_t[2], "expert_units");
     p.sync = i32(work_t[3], "sync");
-    TORCH_CHECK(work_t[2].numel() >= 2 * p.El && work_t[3].numel() >= 4 + p.lay.max_units, "moe_layer: work tensors too small");
+    TORCH_CHECK(work_t[2].numel() >= 2 * p.El && work_t[3].numel() >= 8 + p.lay.max_units, "moe_layer: work tensors too small");
     TORCH_CHECK(p.max_work >= tmoe::moe_layer_max_work(p.bwd, p.lay.max_units, H, p.I, p.El, p.T, (int)reduce_chunk), "moe_layer: work list too small");
     p.group_units = (int)group_units;
     p.lag_percent = (int)lag_percent;
@@ -310,6 +317,13 @@ void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::T
     TORCH_CHECK(bwd ? (gemm_t[6].size(1) == 2 * p.I) : true, "moe_layer: preact shape");
     p.status = opt_status(status);
     p.num_sms = (int)num_sms;
+    if (ok.has_value()) p.geom_ok = i32(*ok, "ok");
+    if (bwd && x_rows.has_value()) {
+        // the kernel rebuilds X in slot space (gemm_t[8]) from one row per received token while the first GEMMs run
+        TORCH_CHECK(x_rows->dim() == 2 && x_rows->size(1) == H, "x_rows must be [rows, H]");
+        p.x_rows = bf16(*x_rows, "x_rows");
+        p.expand_rows = R;
+    }
     if (stats.has_value()) {
         TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == torch::kInt64 && stats->is_contiguous() && stats->numel() >= tmoe::kLayerStatWords,
                     "stats must be a contiguous int64 CUDA tensor of 24 words");
@@ -459,11 +473,14 @@ void register_more(pybind11::module_& m) {
     m.def("route_chunk_tokens", &tmoe::route_chunk_tokens);
     m.def("route_hist", &route_hist);
     m.def("route_scan", &route_scan);
-    m.def("layout_finalize", &layout_finalize);
-    m.def("slot_pad_fill", &slot_pad_fill);
+    m.def("layout_finalize", &layout_finalize, py::arg("meta"), py::arg("rank"), py::arg("N"), py::arg("E"), py::arg("layout"),
+          py::arg("cap_rows") = 0, py::arg("cap_slots") = 0, py::arg("cap_tokens") = 0);
+    m.def("slot_pad_fill", &slot_pad_fill, py::arg("seg_offsets"), py::arg("expert_total_local"), py::arg("slot_row"), py::arg("slot_w"),
+          py::arg("slot_tk"), py::arg("mblock_expert"), py::arg("unit_blk"), py::arg("num_units"), py::arg("ok") = py::none());
     m.def("route_assign", &route_assign);
-    m.def("arrival_order", &arrival_order);
-    m.def("zero_pad_rows", &zero_pad_rows);
+    m.def("arrival_order", &arrival_order, py::arg("meta"), py::arg("rank"), py::arg("N"), py::arg("E"), py::arg("groups"), py::arg("seg_offsets"),
+          py::arg("unit_blk"), py::arg("num_units"), py::arg("blk_group"), py::arg("unit_order"), py::arg("ok") = py::none());
+    m.def("zero_pad_rows", &zero_pad_rows, py::arg("seg_offsets"), py::arg("expert_total_local"), py::arg("slot_x"), py::arg("ok") = py::none());
     m.def("fused_dispatch_gemm", &fused_dispatch_gemm);
     m.def("moe_layer", &moe_layer);
     m.def("moe_layer_max_work", &moe_layer_max_work);

@@ -18,8 +18,9 @@
 //              peer global (plus, in backward, the row's route-weight gradient).  When a rank's last pushed tile is
 //              complete it tells every rank (release store at system scope).
 //   wgrad      backward: the two weight-gradient GEMMs (varlen-K, both operands MN-major) as the tail of the list.
-//   gather     reduce items: once every rank has said that its pushes are complete, sum each token's landed rows in
-//              fp32 and write the output row (backward: also the route-weight gradients).
+//   gather     warps 2 and 3 of every CTA (joined by the epilogue warps when the list is exhausted): once every rank has
+//              said that its pushes are complete, sum each token's landed rows in fp32 and write the output row
+//              (backward: also the route-weight gradients).  In backward this runs under the weight-gradient GEMMs.
 //
 // Reference counterpart: teramoe_fused_forward_kernel / teramoe_fused_backward_kernel with their dispatch, scheduler,
 // compute, combine and gather SM roles (csrc/teramoe/teramoe_orchestrator.cu:2978-3042, :4880-4936, :524-1369,
@@ -47,6 +48,7 @@ constexpr int kSmemBytesL = kBarOffsetL + 512 + 1024;
 constexpr int kDispatchChunkL = 8192;                                     // two per dispatch warp
 constexpr int kPublishBatchL = 4;
 constexpr int kSchedDepthL = 4;
+constexpr int kGatherChunk = 4;                                           // tokens a gather warp claims at a time
 constexpr uint32_t kOffTmemSlot = 112, kOffDispatchBar = 128, kOffSchedFull = 320, kOffSchedEmpty = 352, kOffRing = 384;
 constexpr uint32_t kSchedConsumersL = 2 * kEpiWarps + 2;
 static_assert((kThreads / 32) * 2 * kDispatchChunkL <= kBarOffsetL, "dispatch staging exceeds the operand stages + push staging");
@@ -69,6 +71,14 @@ struct LayerArgs {
     int* item_counter;
     int* push_done;
     int* units_complete;         // units whose first GEMM is complete
+    int* gather_counter;         // next token of the gather role
+    // backward: the gather warps first rebuild X in slot space (operand of dW_gateup) from the rows kept by forward
+    const __nv_bfloat16* x_rows; // [rows, H] one row per received token
+    const int* x_slot_row;       // [slots] row of x_rows that feeds each slot (-1: zero row)
+    __nv_bfloat16* xperm;        // [slots, H]
+    int expand_rows;             // slots to fill
+    int* expand_counter;         // next slot to claim
+    int* expand_done;            // slots filled
     int* unit_done;
     const uint64_t* signal_ptrs;
     const int* my_signal;
@@ -78,6 +88,7 @@ struct LayerArgs {
     const float* gtw_in;
     float* gtw_out;
     unsigned long long* stats;   // optional [kLayerStatWords] time counters (ns summed over the waiting threads), see layer.h
+    const int* geom_ok;          // optional: 0 = the tables were sized too small for this call's layout (every rank sees the same)
     int* status;
 };
 
@@ -138,7 +149,6 @@ __device__ __forceinline__ bool wait_flag_ge_gpu(const int* flag, int target, in
 //   x  bits 0-3 kind, bit 4 "the unit has two blocks", bits 8-27 local expert
 //   first / second GEMM:  y = unit, z = column block | rows awaited in block 0 << 16 | rows awaited in block 1 << 24, w = first block
 //   weight gradients:     y = first slot row of the expert, z = column block | row unit of dW << 16, w = number of 64-row K blocks
-//   reduce:               y = first token, z = number of tokens
 struct ItemGeom {
     int kind, n_blk, group, k0, nk, m0, unit, need;
     bool live;      // this CTA's 128 rows are real
@@ -178,6 +188,7 @@ __device__ __forceinline__ void item_geometry(const LayerArgs& L, const int4& it
 template <bool BWD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 moe_layer_kernel(const __grid_constant__ LayerArgs L) {
+    if (L.geom_ok != nullptr && *L.geom_ok == 0) return;      // before anything is allocated or sent; the host repeats the call
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -338,6 +349,102 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
         cluster_sync_all();                   // both CTAs of the pair are done with the staging buffers: they become operand stages
     }
 
+    // ---------------------------------------------------------------------- gather role
+    // Sums each token's landed rows once every rank has said that its pushes are complete.  Warps 2 and 3 of every CTA
+    // do nothing else (in backward their memory traffic runs under the weight-gradient GEMMs); the epilogue warps join
+    // when the work list is exhausted.  Token chunks come from their own counter.
+    auto expand_loop = [&]() {
+        // X back into slot space, eight rows per claim, four 16-byte loads in flight per lane
+        const int nvec = f.H / 8;
+        while (true) {
+            int s0 = 0;
+            if (lane == 0) s0 = atomicAdd(L.expand_counter, 8);
+            s0 = __shfl_sync(0xffffffffu, s0, 0);
+            if (s0 >= L.expand_rows) break;
+            const int s1 = min(s0 + 8, L.expand_rows);
+            for (int sl = s0; sl < s1; ++sl) {
+                const int rr = L.x_slot_row[sl];
+                int4* dst = reinterpret_cast<int4*>(L.xperm + (long)sl * f.H);
+                if (rr >= 0) {
+                    warp_copy_row(dst, reinterpret_cast<const int4*>(L.x_rows + (long)rr * f.H), nvec, lane);
+                } else {
+                    for (int i = lane; i < nvec; i += 32) dst[i] = make_int4(0, 0, 0, 0);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                fence_acq_rel_gpu();
+                red_add_release_gpu(L.expand_done, s1 - s0);
+            }
+        }
+    };
+    auto gather_loop = [&]() {
+        const int K = f.K, H = f.H, nvec = f.H / 8;
+        if (f.T <= 0) return;
+        {
+            // wait (bounded, slow polling: it may take most of the kernel) for every rank's signal
+            const uint64_t limit_ns = peer_wait_limit_ns(L.status);
+            const uint64_t t0 = globaltimer_ns();
+            while (true) {
+                const bool mine = lane >= L.N || ld_acquire_sys(L.my_signal + lane) >= L.epoch;
+                if (__all_sync(0xffffffffu, mine)) break;
+                if (ld_relaxed_sys(L.status) != 0) return;                    // someone gave up: unwind
+                if (globaltimer_ns() - t0 > limit_ns) {
+                    if (!mine) report_status(L.status, kStatusFlagTimeout, 660 + lane, L.epoch);
+                    return;
+                }
+                __nanosleep(2000);
+            }
+            if (L.stats != nullptr && lane == 0 && warp == 2 && rank == 0) atomicAdd(L.stats + kStatWaitLanded, globaltimer_ns() - t0);
+        }
+        const bool stamps = L.stats != nullptr && lane == 0;
+        if (stamps) atomicMax(L.stats + kStatKindFirst + kWorkReduce, ~globaltimer_ns());
+        while (true) {
+            int t0 = 0;
+            if (lane == 0) t0 = atomicAdd(L.gather_counter, kGatherChunk);
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            if (t0 >= f.T) break;
+            for (int t = t0; t < min(t0 + kGatherChunk, f.T); ++t) {
+                long long e = -1;
+                if (lane < K) e = load_idx_l(f.topk_idx, f.idx_is64, (long)t * K + lane);
+                const bool v = e >= 0 && e < f.E;
+                const uint32_t valid = __ballot_sync(0xffffffffu, v);
+                if constexpr (BWD) {
+                    if (lane < K) L.gtw_out[(long)t * K + lane] = v ? __ldcg(L.gtw_in + (long)t * K + lane) : 0.f;
+                }
+                int4* dst = reinterpret_cast<int4*>(L.out + (long)t * H);
+                const int4* base = reinterpret_cast<const int4*>(L.landing + (long)t * K * H);
+                // Few warps per SM take part, so every lane keeps up to 16 loads in flight: the rows of eight entries
+                // at two positions are all requested before the first is used.  Sum order: k ascending.
+                for (int i = lane; i < nvec; i += 64) {
+                    const bool two = i + 32 < nvec;
+                    float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int k0 = 0; k0 < K; k0 += 8) {
+                        int4 v0[8], v1[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const bool on = (valid >> (k0 + j)) & 1u;
+                            const int4* row = base + (long)(k0 + j) * nvec;
+                            v0[j] = on ? ld_cg_v4(row + i) : make_int4(0, 0, 0, 0);
+                            v1[j] = (on && two) ? ld_cg_v4(row + i + 32) : make_int4(0, 0, 0, 0);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if ((valid >> (k0 + j)) & 1u) {
+                                accum8(a0, v0[j]);
+                                accum8(a1, v1[j]);
+                            }
+                        }
+                    }
+                    dst[i] = pack8(a0);
+                    if (two) dst[i + 32] = pack8(a1);
+                }
+            }
+        }
+        if (stamps) atomicMax(L.stats + kStatKindLast + kWorkReduce, globaltimer_ns());
+    };
+
     // ---------------------------------------------------------------------- worker roles
     {
         const int total_items = min(*L.num_work, L.max_work);
@@ -374,6 +481,7 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                 unsigned long long w_arrive = 0, w_unit = 0, w_wgrad = 0;
                 bool wgrad_ready = false;                    // every unit's first GEMM is complete (checked once per pair)
                 bool wgrad_fenced = false;
+                bool xperm_ready = false;
                 int4 cur = make_int4(-1, 0, 0, 0), nxt = cur;
                 bool have = false, nxt_ready = false;
                 // 1: got an item, 0: none yet (non-blocking form, second CTA), -1: a wait ran out
@@ -423,6 +531,18 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     }
                     // weight gradients: their operands are inputs and outputs of the first GEMM of every unit of the
                     // expert; they sit behind all of them in the list, so one check per pair is enough
+                    if (q.kind == kWorkWgradGateup && !xperm_ready) {
+                        // ... and dW_gateup reads X in slot space, which the gather warps rebuild during the first GEMMs
+                        if (L.xperm != nullptr && ld_acquire_gpu(L.expand_done) < L.expand_rows) {
+                            if (!block) return 0;
+                            const uint64_t t0 = globaltimer_ns();
+                            const bool got = wait_flag_ge_gpu(L.expand_done, L.expand_rows, L.status, 603);
+                            w_wgrad += globaltimer_ns() - t0;
+                            if (!got) return -1;
+                        }
+                        xperm_ready = true;
+                        wgrad_fenced = false;            // one more proxy fence before the first load of X
+                    }
                     if (wgrad_ready) return 1;
                     if (ld_acquire_gpu(L.units_complete) >= num_units) { wgrad_ready = true; return 1; }
                     if (!block) return 0;
@@ -439,7 +559,7 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     have = true;
                     nxt_ready = false;
                     const int k = item_kind(nxt);
-                    if (k >= 0 && k != kWorkReduce) {
+                    if (k >= 0) {
                         ItemGeom qn;
                         item_geometry(L, nxt, rank, qn);
                         nxt_ready = operands_ready(qn, false) == 1;
@@ -458,7 +578,6 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     }
                     const int kind = item_kind(cur);
                     if (kind < 0) break;
-                    if (kind == kWorkReduce) continue;
                     ItemGeom q;
                     item_geometry(L, cur, rank, q);
                     const LayerPhase& P = L.ph[q.kind];
@@ -514,7 +633,6 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
             while (ok) {
                 int4 it;
                 if (!next_item(ss, sph, 652, it) || it.x < 0) break;
-                if (item_kind(it) == kWorkReduce) continue;
                 ItemGeom q;
                 item_geometry(L, it, rank, q);
                 const bool a_mn = q.kind >= kWorkWgradDown;
@@ -561,7 +679,6 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
             uint32_t sph = 0;
             int iter = 0;
             int owed = 0;                 // pushed tiles of this warp that are not yet counted as complete
-            bool landed = false;          // every rank has said that its pushes are complete
             const uint32_t my_row_smem = push_stage_base + (uint32_t)(warp - 4) * kPushWarpBytes + (uint32_t)lane * kPushRowBytes;
             auto flush_pushes = [&]() {
                 if (owed == 0) return;
@@ -580,58 +697,6 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                 if (!next_item(ss, sph, 653, it) || it.x < 0) break;
                 const bool stamps = L.stats != nullptr && warp == 4 && lane == 0 && rank == 0;
                 if (stamps) atomicMax(L.stats + kStatKindFirst + item_kind(it), ~globaltimer_ns());
-                if (item_kind(it) == kWorkReduce) {
-                    flush_pushes();
-                    if (!landed) {
-                        bool mine = true;
-                        const uint64_t t0 = globaltimer_ns();
-                        if (lane < L.N) mine = wait_flag_ge_sys(L.my_signal + lane, L.epoch, L.status, 660 + lane);
-                        landed = __all_sync(0xffffffffu, mine);
-                        if (!landed) { *abort_flag = 1u; ok = false; break; }
-                        if (L.stats != nullptr && lane == 0 && warp == 4) atomicAdd(L.stats + kStatWaitLanded, globaltimer_ns() - t0);
-                    }
-                    const int K = f.K, H = f.H, nvec = f.H / 8;
-                    const int wi = (int)rank * kEpiWarps + (warp - 4);
-                    for (int t = it.y + wi; t < it.y + it.z; t += 2 * kEpiWarps) {
-                        long long e = -1;
-                        if (lane < K) e = load_idx_l(f.topk_idx, f.idx_is64, (long)t * K + lane);
-                        const bool v = e >= 0 && e < f.E;
-                        const uint32_t valid = __ballot_sync(0xffffffffu, v);
-                        if constexpr (BWD) {
-                            if (lane < K) L.gtw_out[(long)t * K + lane] = v ? __ldcg(L.gtw_in + (long)t * K + lane) : 0.f;
-                        }
-                        int4* dst = reinterpret_cast<int4*>(L.out + (long)t * H);
-                        const int4* base = reinterpret_cast<const int4*>(L.landing + (long)t * K * H);
-                        // Few warps per SM take part, so every lane keeps up to 16 loads in flight: the rows of eight entries
-                        // at two positions are all requested before the first is used.  Sum order: k ascending.
-                        for (int i = lane; i < nvec; i += 64) {
-                            const bool two = i + 32 < nvec;
-                            float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                            float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                            for (int k0 = 0; k0 < K; k0 += 8) {
-                                int4 v0[8], v1[8];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    const bool on = (valid >> (k0 + j)) & 1u;
-                                    const int4* row = base + (long)(k0 + j) * nvec;
-                                    v0[j] = on ? ld_cg_v4(row + i) : make_int4(0, 0, 0, 0);
-                                    v1[j] = (on && two) ? ld_cg_v4(row + i + 32) : make_int4(0, 0, 0, 0);
-                                }
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    if ((valid >> (k0 + j)) & 1u) {
-                                        accum8(a0, v0[j]);
-                                        accum8(a1, v1[j]);
-                                    }
-                                }
-                            }
-                            dst[i] = pack8(a0);
-                            if (two) dst[i + 32] = pack8(a1);
-                        }
-                    }
-                    if (stamps) atomicMax(L.stats + kStatKindLast + kWorkReduce, globaltimer_ns());
-                    continue;
-                }
                 ItemGeom q;
                 item_geometry(L, it, rank, q);
                 const GemmArgs& g = L.ph[q.kind].g;
@@ -681,6 +746,12 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
             }
             flush_pushes();
             tma_store_wait<0>();
+            if (ok) gather_loop();            // the list is done: help with the landed rows
+        } else if (warp >= 2) {
+            if constexpr (BWD) {
+                if (L.xperm != nullptr) expand_loop();
+            }
+            gather_loop();
         }
     }
 
@@ -714,9 +785,11 @@ struct ScheduleArgs {
     int max_work;
     int* num_work;
     int2* expert_units;
+    const int* ok;
 };
 
 __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs a) {
+    if (a.ok != nullptr && *a.ok == 0) return;
     const int U = min(*a.num_units, a.max_units);
     const int SG = max(1, a.group_units);
     const int NG = (U + SG - 1) / SG;
@@ -776,10 +849,6 @@ __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs 
         }
         pos += a.El * per_wg;
     }
-    const int nred = (a.T + a.reduce_chunk - 1) / a.reduce_chunk;
-    for (int i = threadIdx.x; i < nred; i += blockDim.x)
-        if (pos + i < a.max_work) a.work[pos + i] = make_int4(kWorkReduce, i * a.reduce_chunk, min(a.reduce_chunk, a.T - i * a.reduce_chunk), 0);
-    pos += nred;
     if (threadIdx.x == 0) *a.num_work = min(pos, a.max_work);
     // units are numbered expert by expert: first unit and unit count of every expert
     for (int e = threadIdx.x; e < a.El; e += blockDim.x) {
@@ -820,7 +889,8 @@ int moe_layer_max_work(int bwd, int max_units, int H, int I, int El, int T, int 
         const int mu_wd = (H + 2 * BM - 1) / (2 * BM), mu_wg = (2 * I + 2 * BM - 1) / (2 * BM);
         n += (long)El * (mu_wd * nbI + mu_wg * nbH);
     }
-    n += (T + reduce_chunk - 1) / reduce_chunk + 1;
+    (void)T; (void)reduce_chunk;
+    n += 1;
     return (int)n;
 }
 
@@ -841,6 +911,7 @@ cudaError_t moe_layer_schedule(const LayerParams& p, cudaStream_t stream) {
     a.T = p.T; a.reduce_chunk = p.reduce_chunk;
     a.work = static_cast<int4*>(p.work); a.max_work = p.max_work; a.num_work = p.num_work;
     a.expert_units = reinterpret_cast<int2*>(p.expert_units);
+    a.ok = p.geom_ok;
     layer_schedule_kernel<<<1, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
@@ -930,7 +1001,16 @@ cudaError_t moe_layer_launch(const LayerParams& p, cudaStream_t stream) {
     L.item_counter = p.sync;
     L.push_done = p.sync + 1;
     L.units_complete = p.sync + 2;
-    L.unit_done = p.sync + 4;
+    L.gather_counter = p.sync + 3;
+    if (p.bwd && p.x_rows != nullptr) {
+        L.x_rows = static_cast<const __nv_bfloat16*>(p.x_rows);
+        L.x_slot_row = p.push.slot_row;
+        L.xperm = static_cast<__nv_bfloat16*>(const_cast<void*>(p.xperm));
+        L.expand_rows = p.expand_rows;
+        L.expand_counter = p.sync + 4;
+        L.expand_done = p.sync + 5;
+    }
+    L.unit_done = p.sync + 8;
     L.signal_ptrs = p.signal_ptrs;
     L.my_signal = p.my_signal;
     L.rank = p.rank; L.N = p.N; L.epoch = p.epoch;
@@ -939,6 +1019,7 @@ cudaError_t moe_layer_launch(const LayerParams& p, cudaStream_t stream) {
     L.gtw_in = p.gtw_in;
     L.gtw_out = p.gtw_out;
     L.stats = p.stats;
+    L.geom_ok = p.geom_ok;
     L.status = p.status;
 
     if ((e = moe_layer_schedule(p, stream)) != cudaSuccess) return e;

@@ -14,13 +14,12 @@ namespace tmoe {
 //   x  bits 0-3 kind, bit 4 "the unit has two blocks", bits 8-27 local expert
 //   first / second GEMM:  y = unit, z = column block | rows awaited in block 0 << 16 | rows awaited in block 1 << 24, w = first block
 //   weight gradients:     y = first slot row of the expert, z = column block | row unit of dW << 16, w = number of 64-row K blocks
-//   reduce:               y = first token, z = number of tokens
 enum LayerWorkKind : int {
     kWorkGemm1 = 0,        // forward: gate_up + SwiGLU    backward: grad_act + dSwiGLU
     kWorkGemm2 = 1,        // forward: down + push         backward: dX + push (+ route gradients)
     kWorkWgradDown = 2,    // backward only
     kWorkWgradGateup = 3,  // backward only
-    kWorkReduce = 4,       // sum the landed rows of a range of tokens
+    kWorkReduce = 4,       // not an item: the gather role (own token counter); the number names its time stamps
 };
 
 // Optional time counters of one launch (nanoseconds, summed over the threads that waited; divide by the number of CTA
@@ -50,6 +49,8 @@ struct LayerParams {
     float* droute_part;            // backward: [out_rows, 2*ceil(I/256)] route-gradient partial sums
     const float* row_w;            // route weight per slot row
     const void* xperm;             // backward: X in slot space [out_rows, H] (operand of dW_gateup)
+    const void* x_rows;            // backward, optional: [rows, H] X once per received token; then the kernel fills xperm itself
+    int expand_rows;               //   (rows 0 .. expand_rows-1, through push.slot_row) while the first GEMMs run
     void* dw_down;                 // backward: [El, H, I]
     void* dw_gateup;               // backward: [El, 2I, H]
     MGroupLayout lay;
@@ -61,7 +62,8 @@ struct LayerParams {
     int max_work;
     int* num_work;                 // device scalar written by the scheduler kernel
     int* expert_units;             // int2 [El]: first unit and unit count of every local expert (written by the scheduler)
-    int* sync;                     // [4 + max_units]: item counter, finished-push counter, complete units, spare, finished first-GEMM warps per unit
+    int* sync;                     // [8 + max_units]: item counter, finished-push counter, complete units, gather token counter, X rows claimed / filled, 2 spare,
+                                   //   finished first-GEMM warps per unit
     int group_units;               // units per batch of the schedule (compute_batch_size / 256)
     int lag_percent;               // how far (percent of a batch) the first GEMM runs ahead before the batch's second GEMM starts
     int min_lag_items;             // lower bound of that distance in first-GEMM items (0: none); about two per CTA pair avoids waiting
@@ -77,6 +79,7 @@ struct LayerParams {
     float* gtw_out;                // backward: [T, K]
     FusedArgs f;                   // dispatch role
     unsigned long long* stats;     // optional [kLayerStatWords], zero before the launch
+    const int* geom_ok;            // optional device flag (layout_finalize): 0 = the layout does not fit the tables, do nothing
     int* status;
     int num_sms;
 };

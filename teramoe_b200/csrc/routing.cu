@@ -89,7 +89,7 @@ route_scan_kernel(const int* chunk_hist, int* chunk_base, int num_chunks, int C,
 }
 
 __global__ void __launch_bounds__(1024)
-layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, LayoutOut o) {
+layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, LayoutOut o, int cap_rows, int cap_slots, int cap_tokens) {
     const int C = E + N + 2;
     const int e_local = E / N;
     __shared__ int sh_spad[64];
@@ -143,6 +143,9 @@ layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, Lay
         o.sizes[5] = lmax;
         o.sizes[6] = my_spad / 128;
         o.sizes[7] = tmax;
+        // capacities the caller sized its tables with before it knew these numbers (0: it waits for them instead);
+        // every rank sees the same maxima, so every rank gets the same answer
+        o.sizes[8] = (cap_rows <= 0 || (rmax <= cap_rows && smax <= cap_slots && tmax <= cap_tokens)) ? 1 : 0;
         o.num_mblocks[0] = my_spad / 128;
         o.seg_offsets[e_local] = my_spad;
         // send order of a fused dispatch: destination ranks in rotation starting with this rank
@@ -167,8 +170,9 @@ layout_finalize_kernel(const int* meta /* [N][C] */, int rank, int N, int E, Lay
 // tables (their offsets depend on the sizes computed by layout_finalize).
 __global__ void __launch_bounds__(256)
 slot_pad_fill_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w, int* slot_tk,
-                     int* mblock_expert, int* unit_blk, int* num_units) {
+                     int* mblock_expert, int* unit_blk, int* num_units, const int* ok) {
     __shared__ int unit_base;
+    if (ok != nullptr && *ok == 0) return;       // the layout does not fit the tables: the caller repeats the call
     for (int le = blockIdx.x; le < e_local; le += gridDim.x) {
         const int first = seg_offsets[le] + expert_total_local[le];
         const int last = seg_offsets[le + 1];
@@ -277,17 +281,18 @@ cudaError_t route_scan(const int* chunk_hist, int* chunk_base, int num_chunks, i
     return cudaGetLastError();
 }
 
-cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const LayoutOut& out, cudaStream_t stream) {
+cudaError_t layout_finalize(const int* meta, int rank, int N, int E, const LayoutOut& out, int cap_rows, int cap_slots, int cap_tokens,
+                            cudaStream_t stream) {
     if (N > 64) return cudaErrorInvalidValue;
-    layout_finalize_kernel<<<1, 1024, 0, stream>>>(meta, rank, N, E, out);
+    layout_finalize_kernel<<<1, 1024, 0, stream>>>(meta, rank, N, E, out, cap_rows, cap_slots, cap_tokens);
     return cudaGetLastError();
 }
 
 cudaError_t slot_pad_fill(const int* seg_offsets, const int* expert_total_local, int e_local, int* slot_row, float* slot_w,
-                          int* slot_tk, int* mblock_expert, int* unit_blk, int* num_units, cudaStream_t stream) {
+                          int* slot_tk, int* mblock_expert, int* unit_blk, int* num_units, const int* ok, cudaStream_t stream) {
     if (e_local <= 0) return cudaSuccess;
     slot_pad_fill_kernel<<<e_local < 256 ? e_local : 256, 256, 0, stream>>>(seg_offsets, expert_total_local, e_local, slot_row, slot_w,
-                                                                            slot_tk, mblock_expert, unit_blk, num_units);
+                                                                            slot_tk, mblock_expert, unit_blk, num_units, ok);
     return cudaGetLastError();
 }
 
@@ -306,7 +311,8 @@ namespace {
 // the units sorted by group.
 __global__ void __launch_bounds__(256)
 arrival_order_kernel(const int* meta, int rank, int N, int E, int groups, const int* seg_offsets, const int* unit_blk,
-                     const int* num_units_p, int max_units, int* blk_group, int* unit_order) {
+                     const int* num_units_p, int max_units, int* blk_group, int* unit_order, const int* ok) {
+    if (ok != nullptr && *ok == 0) return;
     const int C = E + N + 2;
     const int e_local = E / N;
     for (int le = threadIdx.x; le < e_local; le += blockDim.x) {
@@ -344,7 +350,8 @@ arrival_order_kernel(const int* meta, int rank, int N, int E, int groups, const 
 namespace {
 // Pad rows of the slot-space operand table must read as zeros (they take part in the weight gradients).
 __global__ void __launch_bounds__(256)
-zero_pad_rows_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, __nv_bfloat16* slot_x, int H) {
+zero_pad_rows_kernel(const int* seg_offsets, const int* expert_total_local, int e_local, __nv_bfloat16* slot_x, int H, const int* ok) {
+    if (ok != nullptr && *ok == 0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int le = blockIdx.x; le < e_local; le += gridDim.x) {
         const int first = seg_offsets[le] + expert_total_local[le];
@@ -357,17 +364,18 @@ zero_pad_rows_kernel(const int* seg_offsets, const int* expert_total_local, int 
 }
 }  // namespace
 
-cudaError_t zero_pad_rows(const int* seg_offsets, const int* expert_total_local, int e_local, void* slot_x, int H, cudaStream_t stream) {
+cudaError_t zero_pad_rows(const int* seg_offsets, const int* expert_total_local, int e_local, void* slot_x, int H, const int* ok,
+                          cudaStream_t stream) {
     if (e_local <= 0) return cudaSuccess;
     zero_pad_rows_kernel<<<e_local < 512 ? e_local : 512, 256, 0, stream>>>(seg_offsets, expert_total_local, e_local,
-                                                                            static_cast<__nv_bfloat16*>(slot_x), H);
+                                                                            static_cast<__nv_bfloat16*>(slot_x), H, ok);
     return cudaGetLastError();
 }
 
 cudaError_t arrival_order(const int* meta, int rank, int N, int E, int groups, const int* seg_offsets, const int* unit_blk,
-                          const int* num_units, int max_units, int* blk_group, int* unit_order, cudaStream_t stream) {
+                          const int* num_units, int max_units, int* blk_group, int* unit_order, const int* ok, cudaStream_t stream) {
     arrival_order_kernel<<<1, 256, 0, stream>>>(meta, rank, N, E, groups, seg_offsets, unit_blk, num_units, max_units, blk_group,
-                                                unit_order);
+                                                unit_order, ok);
     return cudaGetLastError();
 }
 

@@ -99,6 +99,8 @@ FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4")
 # The whole layer direction as ONE cooperative kernel (csrc/layer.cu): dispatch, both GEMMs, the combine push, the
 # weight gradients (backward) and the reduce run as items of one work list.  "auto": wherever the fused dispatch applies.
 _LAYER_KERNEL_MODE = os.environ.get("TERAMOE_LAYER_KERNEL", "auto")
+# Enqueue the whole forward before the host has read the layout sizes (see EPEngine.layout_gen); "0" waits for them first.
+LAUNCH_AHEAD = os.environ.get("TERAMOE_LAUNCH_AHEAD", "1") == "1"
 LAYER_REDUCE_CHUNK = 64          # tokens per reduce item
 LAYER_MIN_LAG_PER_PAIR = float(os.environ.get("TERAMOE_LAYER_MIN_LAG", "2"))
 
@@ -142,6 +144,8 @@ class LayerHandle:
     unit_order: Optional[torch.Tensor] = None    # fused dispatch: units sorted by arrival group
     fused_dispatch: bool = False
     layer_kernel: bool = False                   # the whole direction runs as one kernel (csrc/layer.cu)
+    pending: Optional[object] = None             # CUDA event behind the copy of the layout sizes, while the host has not read them
+    geom_ok: Optional[torch.Tensor] = None       # device flag: the layout fits the capacities the tables were sized with
     opts: Optional[dict] = None                  # schedule knobs of the layer call (compute_batch_size, ...)
     num_dispatch_sms: int = 0                    # SMs that dispatch first in the fused dispatch + GEMM kernel (0: default)
     unit_blk: Optional[torch.Tensor] = None      # CTA-pair GEMMs: first block of every unit (+ sentinel)
@@ -192,6 +196,7 @@ class EPEngine:
         self.is_cuda = world.is_cuda
         self.ext = world.ext if self.is_cuda else None
         self._trace = None          # list of (phase name, CUDA event) while tracing
+        self._caps = {}             # (T, K, E, N) -> (rows, slots, tokens) capacities learnt from earlier calls (layout_gen)
         self.last_wait_ns = {}      # whole-layer kernel: {0: forward, 1: backward} -> int64[8] wait counters (csrc/layer.h LayerStat)
         self.last_paths = {}
 
@@ -265,8 +270,14 @@ class EPEngine:
         return t
 
     # ------------------------------------------------------------------ routing + dispatch
-    def layout_gen(self, topk_idx: torch.Tensor, num_experts: int):
-        """Counts exchange and deterministic layout.  -> (LayerHandle without receive tables, cuda scratch)."""
+    def layout_gen(self, topk_idx: torch.Tensor, num_experts: int, caps=None):
+        """Counts exchange and deterministic layout.  -> LayerHandle without receive tables.
+
+        The sizes of the layout (rows, slots, maxima over ranks) are computed on the device.  Without `caps` the host
+        waits for them here (one 48-byte read).  With `caps` = (rows, slots, tokens) capacities it does not: the handle
+        comes back with `pending` set, its tables are sized by the capacities, the device flag `geom_ok` tells the
+        kernels whether the layout fits them, and `resolve_sizes` reads the numbers later (behind kernels that are
+        already enqueued, so the GPU never idles while the host catches up)."""
         w = self.world
         N, rank, E = w.size, w.rank, num_experts
         T, K = topk_idx.shape
@@ -301,13 +312,20 @@ class EPEngine:
         yield ("barrier",)
         i32 = dict(dtype=torch.int32, device=dev)
         lay = [torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(E, **i32), torch.empty(N, **i32),
-               torch.empty(N + 1, **i32), torch.empty(El + 1, **i32), torch.empty(2, **i32), torch.empty(8, **i32),
+               torch.empty(N + 1, **i32), torch.empty(El + 1, **i32), torch.empty(2, **i32), torch.empty(12, **i32),
                torch.empty(E, **i32)]
-        ext.layout_finalize(w.meta_view(C), rank, N, E, lay)
+        ext.layout_finalize(w.meta_view(C), rank, N, E, lay, *(caps if caps is not None else (0, 0, 0)))
         w.sizes_host.copy_(lay[7], non_blocking=True)
-        torch.cuda.current_stream(dev).synchronize()
-        w.check_status()
-        R, S, Lr, rmax, smax, lmax, nmb, tmax = w.sizes_host.tolist()
+        pending = None
+        if caps is None:
+            torch.cuda.current_stream(dev).synchronize()
+            w.check_status()
+            R, S, Lr, rmax, smax, lmax, nmb, tmax = w.sizes_host.tolist()[:8]
+        else:
+            pending = torch.cuda.Event()
+            pending.record()
+            rmax, smax, tmax = caps
+            R, S, Lr, lmax, nmb = -1, -1, -1, 0, smax // 128
         send_slot = torch.empty(T, K, **i32)
         send_order = torch.empty(max(T * K, 1), **i32)
         send_row = torch.empty(T, N, **i32)
@@ -323,7 +341,34 @@ class EPEngine:
         h.unit_blk, h.num_units = unit_blk, num_units
         h.send_order, h.num_send = send_order, lay[6][1:2]
         h.num_mblocks = lay[6][0:1]
+        h.pending, h.geom_ok = pending, lay[7][8:9]
         return h
+
+    def resolve_sizes(self, h: LayerHandle) -> bool:
+        """Read the layout sizes of a handle made with capacities (waits for the copy behind layout_finalize, not for
+        the kernels enqueued after it).  False: the layout did not fit; the kernels of the call did nothing and the
+        caller repeats the call with larger capacities (which this records)."""
+        if h.pending is None:
+            return True
+        h.pending.synchronize()
+        h.pending = None
+        R, S, Lr, rmax, smax, lmax, nmb, tmax, ok = self.world.sizes_host.tolist()[:9]
+        self._note_caps(h, (rmax, smax, tmax))
+        if not ok:
+            return False
+        h.rows, h.slots, h.land_rows, h.maxima = R, S, Lr, (rmax, smax, lmax, tmax)
+        return True
+
+    def _caps_key(self, h: LayerHandle):
+        return (h.T, h.K, h.E, h.N)
+
+    def _note_caps(self, h: LayerHandle, seen) -> None:
+        """Capacities for the next call with the same shapes: what was seen plus a margin for the step-to-step change
+        of the routing (slots in whole 128-row blocks); they only grow."""
+        rmax, smax, tmax = seen
+        want = (int(rmax * 1.06) + 64, (int(smax * 1.06) + 127) // 128 * 128 + 256, tmax)
+        old = self._caps.get(self._caps_key(h), (0, 0, 0))
+        self._caps[self._caps_key(h)] = tuple(max(a, b) for a, b in zip(old, want))
 
     def dispatch_gen(self, h: LayerHandle, x: torch.Tensor, topk_weights: Optional[torch.Tensor], with_meta: bool):
         """Push rows (and, with_meta, the slot / row tables) to their destination ranks.  After the
@@ -511,7 +556,11 @@ class EPEngine:
             raise ValueError("weight shapes must be W_gateup [E_local, 2I, H] and W_down [E_local, H, I]")
         num_sms = num_sms or self._grid_sms(impl)
         self._mark("fwd:start")
-        h = yield from self.layout_gen(topk_idx, num_experts)
+        # Calls that will run as one kernel do not wait for the layout sizes: tables are sized by capacities learnt from
+        # earlier calls with these shapes, and the sizes are read while the kernel runs (layout_gen, resolve_sizes).
+        K0 = topk_idx.shape[1]
+        caps = self._caps.get((T, K0, num_experts, w.size)) if (self.is_cuda and use_layer_kernel() and LAUNCH_AHEAD) else None
+        h = yield from self.layout_gen(topk_idx, num_experts, caps=caps)
         self._mark("fwd:routing+layout")
         h.topk_weights = topk_weights
         st = w.status if self.is_cuda else None
@@ -529,11 +578,19 @@ class EPEngine:
         h.layer_kernel = bool(h.fused_dispatch and use_layer_kernel())
         self.last_paths["layer_kernel"] = h.layer_kernel
         if h.layer_kernel:
+            if caps is None and LAUNCH_AHEAD:
+                self._note_caps(h, (h.maxima[0], h.maxima[1], h.maxima[3]))      # the next call with these shapes need not wait
             h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
             h.opts = dict(impl or {})
-            out, preact, saved_x = yield from self.layer_kernel_gen(h, 0, x, topk_weights, W_gateup, W_down, num_sms=num_sms)
+            res = yield from self.layer_kernel_gen(h, 0, x, topk_weights, W_gateup, W_down, num_sms=num_sms)
+            if res is None:
+                # the layout outgrew the capacities: the kernels of this attempt did nothing (on every rank alike)
+                return (yield from self.forward_gen(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, keep_for_backward, impl, num_sms))
+            out, preact, saved_x = res
             saved = SavedForBackward(h, saved_x, preact, stats=self._stats(h, H)) if keep_for_backward else None
             return out, saved
+        if not self.resolve_sizes(h):        # other paths need the sizes on the host: read them, repeat if they did not fit
+            return (yield from self.forward_gen(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, keep_for_backward, impl, num_sms))
         if h.fused_dispatch:
             h.num_dispatch_sms = int((impl or {}).get("num_dispatch_sms", 0))
             tabs, offs, act, preact, _ = yield from self.fused_dispatch_gemm_gen(h, x, topk_weights, W_gateup, 0, num_sms=num_sms,
@@ -682,30 +739,29 @@ class EPEngine:
         offs, total, maxima = _arena_geometry(h.maxima, H, K, True)
         yield ("grow", total)
         tabs = self._tables(offs, maxima, H, K, rows_in.dtype)
-        S = h.slots
+        ahead = h.pending is not None                        # forward only: the host does not know the sizes yet
+        S = h.maxima[1] if ahead else h.slots                # ... so its tensors get the capacity of the slot tables
         R = max(S, 128)                                      # rows of the tensors of this call (the kernel wants >= one block)
+        ok = h.geom_ok if ahead else None
         i32 = dict(dtype=torch.int32, device=dev)
         bf = dict(dtype=torch.bfloat16, device=dev)
         if bwd:
-            xperm = torch.empty(R, H, **bf)
-            if S > 0:
-                ext.expand_rows(saved.saved_x, h.slot_row, xperm, S)          # X back in slot space: operand of dW_gateup
-            self._mark("bwd:expand X")
+            xperm = torch.empty(R, H, **bf)      # X back in slot space (operand of dW_gateup): filled inside the kernel
             yield from self._acquire()                       # no barrier of this call precedes the pushes
         else:
             ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert,
-                              h.unit_blk, h.num_units)
+                              h.unit_blk, h.num_units, ok)
             h.unit_order = torch.zeros(h.unit_blk.numel(), **i32)
             blk_group = torch.zeros(max(S // 128, 1), **i32)
             ext.arrival_order(w.meta_view(E + N + 2), h.rank, N, E, max(1, min(FUSED_DISPATCH_GROUPS, N)), h.seg_offsets, h.unit_blk,
-                              h.num_units, blk_group, h.unit_order)
-        ext.zero_pad_rows(h.seg_offsets, h.expert_total_local, tabs["slot_x"])
+                              h.num_units, blk_group, h.unit_order, ok)
+        ext.zero_pad_rows(h.seg_offsets, h.expert_total_local, tabs["slot_x"], ok)
         out0 = torch.empty(R, I, **bf)
         out1 = torch.empty(R, 2 * I, **bf)
         out = torch.empty(T, H, **bf)
         max_units = h.unit_blk.numel() - 1
         max_work = ext.moe_layer_max_work(bwd, max_units, H, I, El, T, LAYER_REDUCE_CHUNK)
-        work_t = [torch.empty(max_work * 4, **i32), torch.empty(1, **i32), torch.empty(2 * El, **i32), torch.zeros(4 + max_units, **i32)]
+        work_t = [torch.empty(max_work * 4, **i32), torch.empty(1, **i32), torch.empty(2 * El, **i32), torch.zeros(8 + max_units, **i32)]
         layout = [h.mblock_expert, h.num_mblocks, h.unit_blk, h.num_units, h.seg_offsets, h.expert_total_local, h.unit_order]
         send_t = [rows_in, h.topk_idx, h.send_order, h.num_send, h.send_slot.view(-1), h.send_row]
         if bwd:
@@ -739,13 +795,17 @@ class EPEngine:
         wait_ns = torch.zeros(24, dtype=torch.int64, device=dev)
         self.last_wait_ns[kind] = wait_ns
         ext.moe_layer(bwd, gemm_t, layout, send_t, sym_t, offsets, push_t, red_t, work_t, E, N, h.rank, w.next_epoch(),
-                      dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns)
+                      dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns,
+                      saved.saved_x if (bwd and S > 0) else None, ok)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         if bwd:
             self._mark("bwd:layer kernel (dispatch, grad_act, dX + combine, weight gradients, reduce)")
             return out, gtw_out, dW_gateup, dW_down
         self._mark("fwd:layer kernel (dispatch, gate_up, down + combine, reduce)")
+        if not self.resolve_sizes(h):
+            return None
+        S = h.slots
         R_rows = h.rows
         h.slot_row, h.slot_w, h.slot_tk = tabs["slot_row"][:S].clone(), tabs["slot_w"][:S].clone(), tabs["slot_tk"][:S].clone()
         saved_x = torch.empty(R_rows, H, **bf)

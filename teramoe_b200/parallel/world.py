@@ -63,7 +63,7 @@ class EPWorld:
                 self.control = self.ext.SymmetricArena(rank, size, self.control_bytes)
             # status block (csrc/ptx.cuh): words 0-3 error record, words 4-5 the limit (ns) of waits on other ranks
             self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
-            self.sizes_host = torch.zeros(8, dtype=torch.int32).pin_memory()
+            self.sizes_host = torch.zeros(12, dtype=torch.int32).pin_memory()
             self._status_ring = torch.zeros(STATUS_RING, 4, dtype=torch.int32).pin_memory()
             self._status_pending: list = []          # (ring row, event) of status snapshots not looked at yet
             self._status_next = 0
