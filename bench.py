@@ -11,7 +11,14 @@ DeepSeek-V3-like layer (H=7168, I=2048, 32 experts per rank, top-8, 8192 tokens 
 work is fixed as N grows (weak scaling; 256 experts at N=8).  Synthetic data, random-init weights.
 
 Prints ONE JSON line on rank 0.  `value` is the device-timed latency; `e2e` is the same step through the
-public API with every step's inputs copied from pinned host memory and the loss read back.
+public API with every step's inputs (tokens, routing indices, routing weights) copied from pinned host memory,
+the loss computed on the device, its gradient driving the backward pass, and the loss read back by the host.
+
+Other modes (each prints one JSON line on rank 0):
+    --with-baseline   also time the same-box NCCL all_to_all + library grouped-GEMM layer and report the speed-up
+    --check           compare the timed layer's output and gradients with that baseline (numerics_check kernel)
+    --comm            time the un-fused API round trip get_dispatch_layout + deepep_dispatch + deepep_combine
+    --gemm-only       per-kernel TFLOP/s of the grouped tcgen05 GEMMs on the configuration's shapes (one GPU)
 """
 from __future__ import annotations
 
@@ -36,6 +43,12 @@ CONFIGS = {
 # closest published reference number per config (ms, fwd+bwd): docs/latency.md:14, EP16, T=8192, P2M 1.0
 PUBLISHED_MS = {"ref_published": 11.639}
 METRIC = "MoE layer fwd+bwd latency ms (max over ranks)"
+COMM_METRIC = "un-fused dispatch + combine round trip ms (max over ranks)"
+REFERENCE_UNAVAILABLE = (
+    "the reference cannot be installed here: with NVSHMEM (its default) the build needs infiniband/mlx5dv.h, which the image "
+    "lacks; with NVSHMEM disabled the way its setup.py allows, csrc/teramoe/teramoe_orchestrator.cu still includes "
+    "kernels/ibgda_device.cuh and fails on NVSHMEMI_IBGDA_MIN_QP_DEPTH and the nvshmemi_ibgda_* types; its fused path also "
+    "only instantiates 16/32/64 ranks with IBGDA NICs")
 
 
 def parse():
@@ -49,23 +62,79 @@ def parse():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--baseline-loop", action="store_true", help="--impl nccl: per-expert GEMM loop instead of the library grouped GEMM")
     p.add_argument("--trace", action="store_true", help="print per-phase device times (rank 0, stderr) after the timed region")
+    p.add_argument("--with-baseline", action="store_true", help="also time the NCCL all_to_all + grouped-GEMM baseline in this process")
+    p.add_argument("--check", action="store_true", help="compare output and gradients with the NCCL baseline on the bench shape")
+    p.add_argument("--comm", action="store_true", help="time get_dispatch_layout + deepep_dispatch + deepep_combine instead of the layer")
+    p.add_argument("--gemm-only", action="store_true", help="per-kernel GEMM throughput on the configuration's shapes")
     return p.parse_args()
 
 
-def reference_unavailable():
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference does not build offline (nvshmem needs infiniband/mlx5dv.h; third-party/{cutlass,DeepGEMM,quack} "
-                       "submodules are empty) and its fused path only runs on 16/32/64 ranks with IBGDA NICs",
-    }))
+def gemm_only(args, torch, dev):
+    """TFLOP/s of every grouped GEMM kernel on the configuration's per-rank shapes (CUDA events, best of 5 after 2 warm-ups;
+    the operands (several GB) exceed the L2)."""
+    from teramoe_b200.ops import gemm
+
+    H, I, El, K, T, _ = CONFIGS[args.config]
+    if args.tokens:
+        T = args.tokens
+    rows = (T * K // El + 127) // 128 * 128
+    S = rows * El
+    g = torch.Generator(device=dev).manual_seed(7)
+    bf = dict(device=dev, dtype=torch.bfloat16)
+    x = torch.randn(S, H, generator=g, **bf) * 0.1
+    wgu = torch.randn(El, 2 * I, H, generator=g, **bf) * 0.02
+    wd = torch.randn(El, H, I, generator=g, **bf) * 0.02
+    row_w = torch.rand(S, device=dev, generator=g)
+    me = torch.arange(El, device=dev, dtype=torch.int32).repeat_interleave(rows // 128)
+    nmb = torch.tensor([S // 128], device=dev, dtype=torch.int32)
+    offs = torch.arange(El + 1, device=dev, dtype=torch.int32) * rows
+    units = gemm.make_units(me)
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
+
+    def best(fn):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(5):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            e.synchronize()
+            ts.append(s.elapsed_time(e))
+        return min(ts)
+
+    act, preact = gemm.fwd_gateup(x, wgu, row_w, me, nmb, st, units=units)
+    dgu, act_w, _ = gemm.bwd_gradact(x, wd, preact, row_w, me, nmb, st, units=units)
+    table = {}
+    for name, flops, fn in (
+        ("gate_up + SwiGLU", 2.0 * S * 2 * I * H, lambda: gemm.fwd_gateup(x, wgu, row_w, me, nmb, st, units=units)),
+        ("down", 2.0 * S * H * I, lambda: gemm.fwd_down(act, wd, me, nmb, st, units=units)),
+        ("grad_act + dSwiGLU", 2.0 * S * H * I, lambda: gemm.bwd_gradact(x, wd, preact, row_w, me, nmb, st, units=units)),
+        ("dX", 2.0 * S * 2 * I * H, lambda: gemm.bwd_dx(dgu, wgu, me, nmb, st, units=units)),
+        ("dW_down", 2.0 * S * H * I, lambda: gemm.wgrad(x, act_w, offs, El, st, cta_pairs=True)),
+        ("dW_gateup", 2.0 * S * 2 * I * H, lambda: gemm.wgrad(dgu, x, offs, El, st, cta_pairs=True)),
+    ):
+        ms = best(fn)
+        table[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
+    assert st.tolist()[0] == 0
+    print(json.dumps({"metric": "grouped GEMM kernels, TFLOP/s (one GPU, CUDA events, best of 5)", "config": args.config, "rows": S,
+                      "H": H, "I": I, "experts": El, "kernels": table}), flush=True)
 
 
 def main():
     args = parse()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
-            reference_unavailable()
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # host threads and pinned buffers next to this rank's GPU (read-only NVML query + this process's CPU affinity)
+    from teramoe_b200.utils.numa import bind_to_gpu
+    bound = bind_to_gpu(local_rank)
 
     import torch
     import torch.distributed as dist
@@ -73,16 +142,17 @@ def main():
     import teramoe_b200 as tm
     from teramoe_b200 import layout as L
     from teramoe_b200._build import load_ext
+    from teramoe_b200.utils.numerics import numerics_report
     from teramoe_b200.utils.timing import ClockSampler
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.gpus != world:
         if world == 1 and args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with {args.gpus} ranks")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    if args.gemm_only:
+        gemm_only(args, torch, dev)
+        return 0
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -113,84 +183,165 @@ def main():
     Wg = (torch.randn(El, 2 * I, H, device=dev, generator=wgen) * 0.02).to(torch.bfloat16).requires_grad_(True)
     Wd = (torch.randn(El, H, I, device=dev, generator=wgen) * 0.02).to(torch.bfloat16).requires_grad_(True)
 
-    if args.impl == "nccl":
-        from teramoe_b200.parallel.nccl_baseline import NcclMoEBaseline
-        # library grouped GEMMs (torch.nn.functional.grouped_mm) unless --baseline-loop asks for one cuBLAS GEMM per expert
-        layer = NcclMoEBaseline(group, E, grouped=not args.baseline_loop)
-        # the baseline keeps its gate/up weights in the layout a library SwiGLU prefers (gate rows, then up rows)
-        Wg = NcclMoEBaseline.to_chunked(Wg.detach()).requires_grad_(True)
-        run_layer = lambda x, idx, w: layer(x, idx, w, Wg, Wd, chunked=True)
-    else:
-        buf = tm.Buffer(group, int(2e9), int(1e9) if world > 8 else 0, explicitly_destroy=True)
-        run_layer = lambda x, idx, w: buf.teramoe_autograd(x, idx, w, Wg, Wd, E, num_dispatch_sms=32, num_combine_sms=32)
-
-    x_dev, go_dev, idx_dev, w_dev = x_host.to(dev), go_host.to(dev), idx_host.to(dev), w_host.to(dev)
-
-    def step_device():
-        x = x_dev.detach().requires_grad_(True)
-        w = w_dev.detach().requires_grad_(True)
-        out = run_layer(x, idx_dev, w)
-        out.backward(go_dev)
-        Wg.grad = None
-        Wd.grad = None
-        return out
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- activation memory, the reference's protocol (tests/teramoe_test_utils.py:229-252)
-    for _ in range(2):
-        step_device()
-    barrier()
-    torch.cuda.reset_peak_memory_stats()
-    m0 = torch.cuda.memory_allocated()
-    xa = x_dev.detach().requires_grad_(True)
-    wa = w_dev.detach().requires_grad_(True)
-    outa = run_layer(xa, idx_dev, wa)
-    torch.cuda.synchronize()
-    act_mb = (torch.cuda.memory_allocated() - m0) / 2 ** 20
-    outa.backward(go_dev)
-    Wg.grad = None
-    Wd.grad = None
-    del outa, xa, wa
-    peak_mb = (torch.cuda.max_memory_allocated() - m0) / 2 ** 20
+    def make_nccl_layer():
+        from teramoe_b200.parallel.nccl_baseline import NcclMoEBaseline
+        # library grouped GEMMs (torch.nn.functional.grouped_mm) unless --baseline-loop asks for one cuBLAS GEMM per expert
+        layer = NcclMoEBaseline(group, E, grouped=not args.baseline_loop)
+        # the baseline keeps its gate/up weights in the layout a library SwiGLU prefers (gate rows, then up rows)
+        Wgc = NcclMoEBaseline.to_chunked(Wg.detach()).requires_grad_(True)
+        return (lambda x, idx, w: layer(x, idx, w, Wgc, Wd, chunked=True)), Wgc
 
-    # ---- device-timed region: warm-up, then exactly K steps; inputs (weights 2.8 GB/rank) exceed the 126 MB L2
+    buf = None
+    if args.impl == "nccl":
+        run_layer, Wg_used = make_nccl_layer()
+    else:
+        buf = tm.Buffer(group, int(2e9), int(1e9) if world > 8 else 0, explicitly_destroy=True)
+        run_layer = lambda x, idx, w: buf.teramoe_autograd(x, idx, w, Wg, Wd, E, num_dispatch_sms=32, num_combine_sms=32)
+        Wg_used = Wg
+
+    x_dev, go_dev, idx_dev, w_dev = x_host.to(dev), go_host.to(dev), idx_host.to(dev), w_host.to(dev)
+
+    # ------------------------------------------------------------------ un-fused API round trip
+    if args.comm:
+        if buf is None:
+            raise SystemExit("--comm times this library's un-fused API: use --impl teramoe")
+
+        def comm_step():
+            per_rank, _, per_expert, in_rank, _ = buf.get_dispatch_layout(idx_dev, E)
+            recv_x, recv_idx, recv_w, counts, handle, _ = buf.deepep_dispatch(x_dev, topk_idx=idx_dev, topk_weights=w_dev,
+                                                                              num_tokens_per_rank=per_rank, is_token_in_rank=in_rank,
+                                                                              num_tokens_per_expert=per_expert)
+            out, _, _ = buf.deepep_combine(recv_x, handle)
+            return recv_x, out
+
+        for _ in range(max(args.warmup, 3)):
+            comm_step()
+        barrier()
+        sampler = ClockSampler(local_rank).start() if rank == 0 else None
+        l0 = ext.launch_count()
+        s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        from teramoe_b200.utils.timing import flush_l2
+        small = x_dev.numel() * 2 * max(1, min(K, N)) <= 126e6
+        total = 0.0
+        for _ in range(args.steps):
+            if small:
+                flush_l2()              # the payload would stay in L2 from one iteration to the next
+            s_ev.record()
+            recv_x, out = comm_step()
+            e_ev.record()
+            e_ev.synchronize()
+            total += s_ev.elapsed_time(e_ev)
+        barrier()
+        launches = ext.launch_count() - l0
+        ms = reduce_max(total / args.steps)
+        clocks = sampler.stop() if sampler is not None else None
+        rows = recv_x.shape[0]
+        buf.check_status()
+        if rank == 0:
+            print(json.dumps({"metric": COMM_METRIC, "value": round(ms, 4), "unit": "ms", "n_gpus": world, "steps": args.steps,
+                              "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "weak",
+                              "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
+                              "config": {"model": f"moe_layer[{args.config}] H={H} experts={E} top{K}", "tokens_per_rank": T,
+                                         "parallelism": f"ep{world}", "rows_received_rank0": int(rows),
+                                         "l2": ("payload received per rank %.0f MB per transfer; " % (rows * H * 2 / 1e6)) +
+                                               ("larger than the 126 MB L2" if rows * H * 2 > 126e6 else
+                                                "smaller than the 126 MB L2, so 256 MB are overwritten between iterations")},
+                              "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+        buf.destroy()
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    def make_step(layer_fn, Wg_t):
+        def step_device():
+            x = x_dev.detach().requires_grad_(True)
+            w = w_dev.detach().requires_grad_(True)
+            out = layer_fn(x, idx_dev, w)
+            out.backward(go_dev)
+            Wg_t.grad = None
+            Wd.grad = None
+            return out
+        return step_device
+
+    step_device = make_step(run_layer, Wg_used)
+
+    # ---- activation memory, the reference's protocol (tests/teramoe_test_utils.py:229-252)
+    def activation_mb(layer_fn, Wg_t):
+        step = make_step(layer_fn, Wg_t)
+        for _ in range(2):
+            step()
+        barrier()
+        torch.cuda.reset_peak_memory_stats()
+        m0 = torch.cuda.memory_allocated()
+        xa = x_dev.detach().requires_grad_(True)
+        wa = w_dev.detach().requires_grad_(True)
+        outa = layer_fn(xa, idx_dev, wa)
+        torch.cuda.synchronize()
+        act = (torch.cuda.memory_allocated() - m0) / 2 ** 20
+        outa.backward(go_dev)
+        Wg_t.grad = None
+        Wd.grad = None
+        del outa, xa, wa
+        return act, (torch.cuda.max_memory_allocated() - m0) / 2 ** 20
+
+    act_mb, peak_mb = activation_mb(run_layer, Wg_used)
+
+    def time_steps(step, steps, warmup):
+        """Warm-up, then exactly `steps` steps between two events; inputs (weights, GBs per rank) exceed the 126 MB L2."""
+        for _ in range(warmup):
+            step()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        wall0 = time.perf_counter()
+        evs[0].record()
+        for i in range(steps):
+            step()
+            evs[i + 1].record()
+        barrier()
+        wall = (time.perf_counter() - wall0) * 1e3 / steps
+        return evs[0].elapsed_time(evs[-1]) / steps, [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)], wall
+
+    # ---- device-timed region
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    l0 = ext.launch_count()
     for _ in range(max(args.warmup, 3)):
         step_device()
     barrier()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     l0 = ext.launch_count()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    wall0 = time.perf_counter()
-    evs[0].record()
-    for i in range(args.steps):
-        step_device()
-        evs[i + 1].record()
-    barrier()
-    wall_ms = (time.perf_counter() - wall0) * 1e3
-    launches = (ext.launch_count() - l0)
-    total_ms = evs[0].elapsed_time(evs[-1])
-    per_step = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
-    ms = total_ms / args.steps
+    ms, per_step, wall_ms = time_steps(step_device, args.steps, 0)
+    launches = ext.launch_count() - l0
+    if buf is not None:
+        buf.check_status()          # a device-side wait that ran out anywhere in the timed steps raises here
 
-    # ---- end to end through the public API: every step copies its inputs from pinned host memory
-    # (prefetched on a copy stream, double-buffered) and reads the loss back to the host
+    # ---- end to end through the public API: every step copies its inputs (tokens, routing) from pinned host memory
+    # (prefetched on a copy stream, double-buffered), computes a loss on the device whose gradient drives the backward
+    # pass, and hands the loss to the host
     e2e = None
     if not args.no_e2e:
         copy_stream = torch.cuda.Stream()
-        slots = [[torch.empty_like(x_dev), torch.empty_like(go_dev), torch.empty_like(idx_dev), torch.empty_like(w_dev)] for _ in range(2)]
+        slots = [[torch.empty_like(x_dev), torch.empty_like(idx_dev), torch.empty_like(w_dev)] for _ in range(2)]
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
         loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+        inv_n = 1.0 / float(max(T * H, 1))
 
         def prefetch(i):
             s = i % 2
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(consumed[s])
-                for d, h in zip(slots[s], (x_host, go_host, idx_host, w_host)):
+                for d, h in zip(slots[s], (x_host, idx_host, w_host)):
                     d.copy_(h, non_blocking=True)
                 ready[s].record(copy_stream)
 
@@ -200,14 +351,14 @@ def main():
             cur.wait_event(ready[s])
             if i + 1 < n:
                 prefetch(i + 1)
-            xd, god, idxd, wd = slots[s]
+            xd, idxd, wd = slots[s]
             x = xd.detach().requires_grad_(True)
             w = wd.detach().requires_grad_(True)
             out = run_layer(x, idxd, w)
-            loss = (out * god).sum(dtype=torch.float32) / out.numel()      # scalar the host reads back every step
-            out.backward(god)
+            loss = out.float().square().sum() * (0.5 * inv_n)       # scalar the host reads back every step
+            loss.backward()
             consumed[s].record(cur)
-            Wg.grad = None
+            Wg_used.grad = None
             Wd.grad = None
             loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
             return loss_host
@@ -233,11 +384,45 @@ def main():
         barrier()
         e2e_wall = (time.perf_counter() - t0) * 1e3 / args.steps
         e2e_ms = max(s_ev.elapsed_time(e_ev) / args.steps, 0.0)
-        h2d = sum(t.numel() * t.element_size() for t in (x_host, go_host, idx_host, w_host))
+        h2d = sum(t.numel() * t.element_size() for t in (x_host, idx_host, w_host))
         e2e = {"ms": e2e_ms, "wall_ms": e2e_wall, "h2d": h2d, "d2h": 4}
+        if buf is not None:
+            buf.check_status()
 
     clocks = sampler.stop() if sampler is not None else None
-    if args.trace and args.impl == "teramoe":
+
+    # ---- the same-box baseline (NCCL all_to_all_single + library grouped GEMMs) in this process, same inputs
+    baseline = None
+    check = None
+    if (args.with_baseline or args.check) and args.impl == "teramoe":
+        nccl_layer, Wgc = make_nccl_layer()
+        if args.check:
+            def grads(layer_fn, Wg_t):
+                x = x_dev.detach().requires_grad_(True)
+                w = w_dev.detach().requires_grad_(True)
+                out = layer_fn(x, idx_dev, w)
+                out.backward(go_dev)
+                res = {"out": out.detach(), "dx": x.grad, "dw": w.grad, "dWd": Wd.grad.clone(),
+                       "dWg": Wg_t.grad.clone()}
+                Wg_t.grad = None
+                Wd.grad = None
+                return res
+            ours, theirs = grads(run_layer, Wg), grads(nccl_layer, Wgc)
+            from teramoe_b200.parallel.nccl_baseline import NcclMoEBaseline
+            theirs["dWg"] = torch.stack([theirs["dWg"][:, :I], theirs["dWg"][:, I:]], dim=2).reshape(El, 2 * I, H)   # back to interleaved rows
+            check = {}
+            for name in ("out", "dx", "dw", "dWg", "dWd"):
+                r = numerics_report(ours[name].float().contiguous(), theirs[name].float().contiguous())
+                check[name] = {k: float(f"{v:.3e}") for k, v in r.items()}
+                check[name]["ok"] = bool(r["calc_diff"] <= 1e-4 and r["cosine"] >= 0.99)
+            del ours, theirs
+        if args.with_baseline:
+            nccl_step = make_step(nccl_layer, Wgc)
+            b_act, _ = activation_mb(nccl_layer, Wgc)
+            b_ms, _, _ = time_steps(nccl_step, args.steps, max(args.warmup, 3))
+            baseline = {"ms": reduce_max(b_ms), "activation_mb": reduce_max(b_act)}
+
+    if args.trace and buf is not None:
         buf.trace(True)
         for _ in range(3):
             step_device()
@@ -249,14 +434,13 @@ def main():
             for k, v in rep.items():
                 print(f"  {k:40s} {v:8.3f}", file=sys.stderr)
             print(f"  {'sum':40s} {tot:8.3f}", file=sys.stderr)
-            print("wait times inside the layer kernels (ms per CTA pair):", buf._engine.wait_report(), file=sys.stderr)
-
-    def reduce_max(v):
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    waits = buf._engine.wait_report() if buf is not None else None
+    if args.trace and waits and world > 1:
+        allw = [None] * world
+        dist.all_gather_object(allw, waits)
+        waits = {"per_rank": allw}
+    if args.trace and rank == 0:
+        print("wait times inside the layer kernels (ms per CTA pair):", waits, file=sys.stderr)
 
     ms_max = reduce_max(ms)
     act_max = reduce_max(act_mb)
@@ -282,21 +466,30 @@ def main():
             "config": {"model": f"moe_layer[{args.config}] H={H} I={I} experts/rank={El} experts={E} top{K}", "global_batch": T * world,
                        "seq_len": T, "tokens_per_rank": T, "parallelism": f"ep{world}", "peak_to_mean": p2m,
                        "l2": "inputs larger than L2 (expert weights %.1f GB per rank are re-read every step)" % (El * 3 * H * I * 2 / 1e9)},
-            "paths": (dict(getattr(buf._engine, "last_paths", {})) if args.impl == "teramoe" else None),
+            "paths": (dict(getattr(buf._engine, "last_paths", {})) if buf is not None else None),
             "tokens_per_s": round(T * world / (ms_max * 1e-3), 1),
             "tflops_per_gpu": round(flops / (ms_max * 1e-3) / 1e12, 1),
             "activation_mb": round(act_max, 2),
             "peak_mb": round(peak_mb, 2),
             "ms_per_step_rank0_min": round(min(per_step), 4),
-            "wall_ms_per_step": round(wall_ms / args.steps, 4),
+            "wall_ms_per_step": round(wall_ms, 4),
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "cpu_binding": (f"{len(bound)} CPUs local to the GPU" if bound else "unbound"),
         }
         if e2e:
             out["e2e"] = {"value": round(e2e_max, 4), "unit": "ms", "wall_ms": round(e2e_wall_max, 4),
                           "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])}
+        if baseline is not None:
+            out["same_box_nccl_baseline"] = {"ms": round(baseline["ms"], 4), "speedup": round(baseline["ms"] / ms_max, 3),
+                                             "activation_mb": round(baseline["activation_mb"], 2),
+                                             "activation_saving": round(1.0 - act_max / max(baseline["activation_mb"], 1e-9), 3)}
+        if check is not None:
+            out["check_vs_nccl_baseline"] = check
+        if waits is not None and "per_rank" not in waits:
+            out["layer_kernel_waits_ms_per_pair"] = {k: {n: v for n, v in d.items() if n != "spans_ms"} for k, d in waits.items()}
         print(json.dumps(out), flush=True)
-    if args.impl != "nccl":
+    if buf is not None:
         buf.destroy()
     if world > 1:
         dist.destroy_process_group()

@@ -254,18 +254,19 @@ class Buffer(LowLatencyMixin):
             T, K = topk_idx.shape
             El = num_experts // N
             if topk_idx.is_cuda:
+                # two kernels, nothing else: per-chunk histograms (which also write is_token_in_rank), then their column sums
                 ext = self._world.ext
                 C = num_experts + N + 2
                 chunk = ext.route_chunk_tokens()
                 chunks = max(1, (T + chunk - 1) // chunk)
-                hist = torch.zeros(chunks * C, dtype=torch.int32, device=topk_idx.device)
+                dev = topk_idx.device
+                hist = torch.zeros(chunks * C, dtype=torch.int32, device=dev) if T == 0 else torch.empty(chunks * C, dtype=torch.int32, device=dev)
+                in_rank = torch.empty(T, N, dtype=torch.bool, device=dev)
                 if T > 0:
-                    ext.route_hist(topk_idx.contiguous(), num_experts, N, hist)
-                tot = hist.view(chunks, C).sum(0, dtype=torch.int32)
-                per_expert, per_rank = tot[:num_experts].contiguous(), tot[num_experts:num_experts + N].contiguous()
-                valid = (topk_idx >= 0) & (topk_idx < num_experts)
-                d = torch.where(valid, topk_idx // El, torch.zeros_like(topk_idx)).long()
-                in_rank = torch.zeros(T, N, dtype=torch.int32, device=topk_idx.device).scatter_reduce_(1, d, valid.int(), reduce="amax").bool()
+                    ext.route_hist(topk_idx.contiguous(), num_experts, N, hist, in_rank)
+                tot = torch.empty(C, dtype=torch.int32, device=dev)
+                ext.route_sum(hist, chunks, C, tot)
+                per_expert, per_rank = tot[:num_experts], tot[num_experts:num_experts + N]
             else:
                 from . import layout as L
                 row = L.count_row(topk_idx, num_experts, N)
@@ -317,23 +318,18 @@ class Buffer(LowLatencyMixin):
             E = num_experts if num_experts is not None else (int(num_tokens_per_expert.numel()) if num_tokens_per_expert is not None else None)
             if E is None:
                 raise ValueError("pass num_tokens_per_expert (from get_dispatch_layout) or num_experts")
+            if num_worst_tokens > 0 and x.is_cuda:
+                return self._dispatch_fixed_shape(x, topk_idx.contiguous(), topk_weights.float().contiguous(), E, num_worst_tokens)
             h = self._drive(eng.layout_gen(topk_idx.contiguous(), E))
             h.topk_weights = topk_weights
             tabs, _ = self._drive(eng.dispatch_gen(h, x, topk_weights.float().contiguous(), with_meta=True))
             eng.snapshot_tables(h, tabs)
-            recv_x = tabs["recv_x"][: h.rows].clone()
-            self._release()
             R, K = h.rows, h.K
-            rs = h.row_slots.long()
-            valid = rs >= 0
-            sl = rs.clamp(min=0)
-            kpos = (h.slot_tk.long()[sl] % K)
-            recv_idx = torch.full((R, K), -1, dtype=topk_idx.dtype, device=x.device)
-            recv_w = torch.zeros(R, K, dtype=torch.float32, device=x.device)
-            rr = torch.arange(R, device=x.device).view(R, 1).expand(R, K)
-            le = h.mblock_expert.long()[sl // 128] if h.slots > 0 else sl
-            recv_idx[rr[valid], kpos[valid]] = le[valid].to(topk_idx.dtype)
-            recv_w[rr[valid], kpos[valid]] = h.slot_w[sl[valid]]
+            # the sender's dispatch kernel wrote these next to the rows (csrc/comm.cu dispatch_push)
+            recv_x = tabs["recv_x"][:R].clone()
+            recv_idx = tabs["row_topk_idx"][:R].to(topk_idx.dtype, copy=True)
+            recv_w = tabs["row_topk_w"][:R].clone()
+            self._release()
             if num_worst_tokens > 0:
                 # fixed-shape mode (csrc/deep_ep.cpp:377-386): outputs have `num_worst_tokens` rows, rows past the
                 # received count are zero with expert id -1, and no per-expert list is produced
@@ -350,6 +346,30 @@ class Buffer(LowLatencyMixin):
 
         res, ev = self._on_comm_stream(run, previous_event, async_finish, allocate_on_comm_stream)
         return (*res, ev)
+
+    def _dispatch_fixed_shape(self, x, topk_idx, topk_weights, E, worst):
+        """Dispatch with `num_worst_tokens` rows of output and NO host wait (csrc/kernels/intranode.cu:521-531 in the
+        reference): the receive tables are sized for `worst` rows, the layout sizes stay on the device, rows past the
+        received count are filled with "nothing" by a kernel that reads the count there, and the handle learns the sizes
+        when a later call (deepep_combine) asks for them.  If more than `worst` rows would arrive anywhere, nothing is
+        sent and that later call raises."""
+        eng, K = self._engine, topk_idx.shape[1]
+        El = E // self.group_size
+        if x.shape[0] > worst:
+            raise ValueError(f"{x.shape[0]} tokens exceed num_worst_tokens={worst}")
+        slots_cap = (worst * min(K, El) + 127) // 128 * 128 + 128 * El
+        h = self._drive(eng.layout_gen(topk_idx, E, caps=(worst, slots_cap, worst)))
+        h.topk_weights = topk_weights
+        tabs, _ = self._drive(eng.dispatch_gen(h, x, topk_weights, with_meta=True))
+        eng.snapshot_tables(h, tabs)
+        recv_x = tabs["recv_x"][:worst].clone()
+        recv_idx = tabs["row_topk_idx"][:worst].clone()
+        recv_w = tabs["row_topk_w"][:worst].clone()
+        self._release()
+        self._world.ext.tail_fill(recv_x, recv_idx, recv_w, h.recv_row_base[self.group_size:])
+        if topk_idx.dtype != torch.int64:
+            recv_idx = recv_idx.to(topk_idx.dtype)
+        return recv_x, recv_idx, recv_w, [], h
 
     def deepep_combine(self, x: torch.Tensor, handle: LayerHandle, topk_weights: Optional[torch.Tensor] = None, bias=None,
                        config: Optional[Config] = None, previous_event: Optional[EventOverlap] = None, async_finish: bool = False,

@@ -75,17 +75,29 @@ tmoe::LayoutOut layout_out(const std::vector<torch::Tensor>& t) {
 }
 
 tmoe::SymOffsets sym_offsets(const std::vector<int64_t>& v) {
-    TORCH_CHECK(v.size() == 9, "need 9 symmetric offsets");
+    TORCH_CHECK(v.size() == 11, "need 11 symmetric offsets");
     tmoe::SymOffsets so;
     so.recv_x = v[0]; so.slot_row = v[1]; so.slot_w = v[2]; so.slot_tk = v[3]; so.row_tok = v[4];
-    so.row_land = v[5]; so.row_slots = v[6]; so.landing = v[7]; so.gtw = v[8];
+    so.row_land = v[5]; so.row_slots = v[6]; so.landing = v[7]; so.gtw = v[8]; so.row_topk_idx = v[9]; so.row_topk_w = v[10];
     return so;
 }
 
-void route_hist(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_hist) {
+void route_hist(torch::Tensor topk_idx, int64_t E, int64_t N, torch::Tensor chunk_hist, c10::optional<torch::Tensor> in_rank) {
     const TopK tk = topk(topk_idx);
+    uint8_t* ir = nullptr;
+    if (in_rank.has_value()) {
+        TORCH_CHECK(in_rank->is_cuda() && in_rank->scalar_type() == torch::kBool && in_rank->is_contiguous() &&
+                    in_rank->numel() == (int64_t)tk.T * N, "in_rank must be a contiguous bool [T, N] CUDA tensor");
+        ir = reinterpret_cast<uint8_t*>(in_rank->data_ptr<bool>());
+    }
     c10::cuda::CUDAGuard guard(topk_idx.device());
-    TM_CHECK_CUDA(tmoe::route_hist(tk.ptr, tk.is64, tk.T, tk.K, (int)E, (int)N, i32(chunk_hist, "chunk_hist"), cur_stream()));
+    TM_CHECK_CUDA(tmoe::route_hist(tk.ptr, tk.is64, tk.T, tk.K, (int)E, (int)N, i32(chunk_hist, "chunk_hist"), ir, cur_stream()));
+}
+
+void route_sum(torch::Tensor chunk_hist, int64_t num_chunks, int64_t C, torch::Tensor totals) {
+    TORCH_CHECK(chunk_hist.numel() >= num_chunks * C && totals.numel() >= C, "route_sum: sizes");
+    c10::cuda::CUDAGuard guard(chunk_hist.device());
+    TM_CHECK_CUDA(tmoe::route_sum(i32(chunk_hist, "chunk_hist"), (int)num_chunks, (int)C, i32(totals, "totals"), cur_stream()));
 }
 
 void route_scan(torch::Tensor chunk_hist, torch::Tensor chunk_base, int64_t num_chunks, int64_t E, int64_t rank, int64_t N,
@@ -372,14 +384,22 @@ void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoc
 
 void dispatch_push(torch::Tensor x, torch::Tensor topk_idx, torch::Tensor topk_w, int64_t E, int64_t N, torch::Tensor send_slot,
                    torch::Tensor send_row, torch::Tensor land_off, torch::Tensor arena_ptrs, std::vector<int64_t> offsets,
-                   bool with_meta, int64_t num_blocks) {
+                   bool with_meta, int64_t num_blocks, c10::optional<torch::Tensor> ok) {
     const TopK tk = topk(topk_idx);
     TORCH_CHECK(x.dim() == 2 && x.size(0) == tk.T, "x must be [T,H]");
     c10::cuda::CUDAGuard guard(x.device());
     TM_CHECK_CUDA(tmoe::dispatch_push(bf16(x, "x"), tk.ptr, tk.is64, f32(topk_w, "topk_weights"), tk.T, tk.K, (int)x.size(1), (int)E, (int)N,
                                       i32(send_slot, "send_slot"), i32(send_row, "send_row"), i32(land_off, "land_off"),
                                       u64(arena_ptrs, "arena_ptrs"), sym_offsets(offsets), with_meta ? 1 : 0, (int)num_blocks,
-                                      cur_stream()));
+                                      ok.has_value() ? i32(*ok, "ok") : nullptr, cur_stream()));
+}
+
+void tail_fill(torch::Tensor x, torch::Tensor idx, torch::Tensor w, torch::Tensor rows_dev) {
+    TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == torch::kInt64 && idx.is_contiguous() && idx.dim() == 2 && idx.size(0) == x.size(0) &&
+                w.sizes() == idx.sizes(), "tail_fill: idx must be int64 [rows, K] and w fp32 [rows, K]");
+    c10::cuda::CUDAGuard guard(x.device());
+    TM_CHECK_CUDA(tmoe::tail_fill(bf16(x, "x"), idx.data_ptr<int64_t>(), f32(w, "w"), i32(rows_dev, "rows"), (int)x.size(0), (int)x.size(1),
+                                  (int)idx.size(1), cur_stream()));
 }
 
 void expand_rows(torch::Tensor rows, torch::Tensor slot_row, torch::Tensor out, int64_t num_slots) {
@@ -471,7 +491,8 @@ torch::Tensor arena_view(tmoe::SymmetricArena& arena, int64_t offset, std::vecto
 
 void register_more(pybind11::module_& m) {
     m.def("route_chunk_tokens", &tmoe::route_chunk_tokens);
-    m.def("route_hist", &route_hist);
+    m.def("route_hist", &route_hist, py::arg("topk_idx"), py::arg("E"), py::arg("N"), py::arg("chunk_hist"), py::arg("in_rank") = py::none());
+    m.def("route_sum", &route_sum);
     m.def("route_scan", &route_scan);
     m.def("layout_finalize", &layout_finalize, py::arg("meta"), py::arg("rank"), py::arg("N"), py::arg("E"), py::arg("layout"),
           py::arg("cap_rows") = 0, py::arg("cap_slots") = 0, py::arg("cap_tokens") = 0);
@@ -487,7 +508,10 @@ void register_more(pybind11::module_& m) {
     m.def("moe_layer_schedule", &moe_layer_schedule);
     m.def("ep_barrier", &ep_barrier, py::arg("signal_ptrs"), py::arg("rank"), py::arg("N"), py::arg("epoch"), py::arg("status"),
           py::arg("site"), py::arg("limit_ms"), py::arg("mode") = 0);
-    m.def("dispatch_push", &dispatch_push);
+    m.def("dispatch_push", &dispatch_push, py::arg("x"), py::arg("topk_idx"), py::arg("topk_w"), py::arg("E"), py::arg("N"), py::arg("send_slot"),
+          py::arg("send_row"), py::arg("land_off"), py::arg("arena_ptrs"), py::arg("offsets"), py::arg("with_meta"), py::arg("num_blocks"),
+          py::arg("ok") = py::none());
+    m.def("tail_fill", &tail_fill);
     m.def("expand_rows", &expand_rows);
     m.def("combine_push", &combine_push);
     m.def("combine_reduce", &combine_reduce);

@@ -51,7 +51,8 @@ __device__ __forceinline__ int64_t load_topk(const void* idx, int is64, long i) 
 __global__ void __launch_bounds__(256)
 dispatch_push_kernel(const __nv_bfloat16* x, const void* topk_idx, int is64, const float* topk_w, int T, int K, int H, int E,
                      int N, const int* send_slot, const int* send_row, const int* land_off, const uint64_t* arena_ptrs,
-                     SymOffsets so, int with_meta) {
+                     SymOffsets so, int with_meta, const int* ok) {
+    if (ok != nullptr && *ok == 0) return;       // the layout does not fit the receivers' tables (fixed-shape mode): send nothing
     const int lane = threadIdx.x & 31;
     const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
     const int e_local = E / N;
@@ -102,6 +103,26 @@ dispatch_push_kernel(const __nv_bfloat16* x, const void* topk_idx, int is64, con
                 const uint64_t base = arena_ptrs[lane];
                 reinterpret_cast<int*>(base + so.row_tok)[my_row] = t;
                 reinterpret_cast<int*>(base + so.row_land)[my_row] = lo + __popc(mask & ((1u << lane) - 1u));
+            }
+            // what the receiver hands out as recv_topk_idx / recv_topk_weights: lane k writes entry k of the token's row on
+            // every rank the token goes to (local expert id and weight where the entry's expert lives there, -1 / 0 elsewhere)
+            {
+                int64_t e_k = -1;
+                float w_k = 0.f;
+                if (lane < K) {
+                    e_k = load_topk(topk_idx, is64, (long)t * K + lane);
+                    if (e_k < 0 || e_k >= E) e_k = -1;
+                    else w_k = topk_w[(long)t * K + lane];
+                }
+                for (uint32_t m = mask; m != 0; m &= m - 1) {
+                    const int d = __ffs(m) - 1;
+                    const int row = __shfl_sync(0xffffffffu, my_row, d);
+                    if (lane < K) {
+                        const bool here = e_k >= 0 && (int)e_k / e_local == d;
+                        reinterpret_cast<int64_t*>(arena_ptrs[d] + so.row_topk_idx)[(long)row * K + lane] = here ? e_k - (int64_t)d * e_local : -1;
+                        reinterpret_cast<float*>(arena_ptrs[d] + so.row_topk_w)[(long)row * K + lane] = here ? w_k : 0.f;
+                    }
+                }
             }
         }
     }
@@ -207,6 +228,23 @@ combine_reduce_kernel(const __nv_bfloat16* landing, const int* land_off, const i
                 for (int j = 0; j < n; ++j) accum_bf16x8(acc, ld_nc_v4(reinterpret_cast<const int4*>(landing + (lo + j) * H) + i));
                 dst[i] = pack_bf16x8(acc);
             }
+        }
+    }
+}
+
+// Fixed-shape dispatch outputs: rows past the received count (a device scalar) read as "nothing": zero payload,
+// expert id -1, weight 0.  One warp per row.
+__global__ void __launch_bounds__(256)
+tail_fill_kernel(__nv_bfloat16* x, int64_t* idx, float* w, const int* rows_dev, int total_rows, int H, int K) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+    const int first = max(0, min(*rows_dev, total_rows));
+    for (int r = first + ((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < total_rows; r += warps_per_grid) {
+        int4* row = reinterpret_cast<int4*>(x + (long)r * H);
+        for (int i = lane; i < H / 8; i += 32) row[i] = make_int4(0, 0, 0, 0);
+        if (lane < K) {
+            idx[(long)r * K + lane] = -1;
+            w[(long)r * K + lane] = 0.f;
         }
     }
 }
@@ -345,12 +383,19 @@ cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, 
 
 cudaError_t dispatch_push(const void* x, const void* topk_idx, int is64, const float* topk_w, int T, int K, int H, int E, int N,
                           const int* send_slot, const int* send_row, const int* land_off, const uint64_t* arena_ptrs,
-                          const SymOffsets& so, int with_meta, int num_blocks, cudaStream_t stream) {
+                          const SymOffsets& so, int with_meta, int num_blocks, const int* ok, cudaStream_t stream) {
     if (T == 0) return cudaSuccess;
     if (K > 32 || N > 32 || H % 8 != 0) return cudaErrorInvalidValue;
     const int grid = num_blocks > 0 ? num_blocks : grid_for_warps(T, 256);
     dispatch_push_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), topk_idx, is64, topk_w, T, K, H, E, N,
-                                                   send_slot, send_row, land_off, arena_ptrs, so, with_meta);
+                                                   send_slot, send_row, land_off, arena_ptrs, so, with_meta, ok);
+    return cudaGetLastError();
+}
+
+cudaError_t tail_fill(void* x, int64_t* idx, float* w, const int* rows_dev, int total_rows, int H, int K, cudaStream_t stream) {
+    if (total_rows == 0) return cudaSuccess;
+    if (K > 32 || H % 8 != 0) return cudaErrorInvalidValue;
+    tail_fill_kernel<<<grid_for_warps(total_rows, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(x), idx, w, rows_dev, total_rows, H, K);
     return cudaGetLastError();
 }
 

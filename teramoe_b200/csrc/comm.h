@@ -16,6 +16,8 @@ struct SymOffsets {
     uint64_t row_slots;  // [row_cap, K] int    slots of the row's local expert hits (-1 padded)
     uint64_t landing;    // [land_cap, H] bf16  combine landing rows (one per token and destination rank)
     uint64_t gtw;        // [tok_cap*K] float   route-weight gradients arriving from expert ranks
+    uint64_t row_topk_idx;  // [row_cap, K] int64  LOCAL expert id of each of the row's top-k entries, -1 for experts of other ranks
+    uint64_t row_topk_w;    // [row_cap, K] float  route weight of those entries, 0 elsewhere
 };
 
 // limit_ms <= 0 selects the run-time limit of the status block (ptx.cuh).
@@ -26,7 +28,11 @@ cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, 
 
 cudaError_t dispatch_push(const void* x, const void* topk_idx, int is64, const float* topk_w, int T, int K, int H, int E, int N,
                           const int* send_slot, const int* send_row, const int* land_off, const uint64_t* arena_ptrs,
-                          const SymOffsets& so, int with_meta, int num_blocks, cudaStream_t stream);
+                          const SymOffsets& so, int with_meta, int num_blocks, const int* ok /* optional device flag, 0: send nothing */,
+                          cudaStream_t stream);
+
+// Rows [*rows_dev, total_rows) of fixed-shape dispatch outputs become "nothing": zero payload, expert id -1, weight 0.
+cudaError_t tail_fill(void* x, int64_t* idx, float* w, const int* rows_dev, int total_rows, int H, int K, cudaStream_t stream);
 
 cudaError_t expand_rows(const void* rows, const int* slot_row, void* out, int num_slots, int H, cudaStream_t stream);
 

@@ -35,7 +35,7 @@ __device__ __forceinline__ int64_t load_topk(const void* idx, int is64, long i) 
 
 // columns of a histogram row: [0,E) experts, [E,E+N) destination ranks, E+N = sum of distinct ranks, E+N+1 = tokens
 __global__ void __launch_bounds__(kChunkTokens)
-route_hist_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist) {
+route_hist_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, uint8_t* in_rank /* [T,N] bool or null */) {
     extern __shared__ int sh[];
     const int C = E + N + 2;
     const int e_local = E / N;
@@ -51,13 +51,24 @@ route_hist_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, in
                 mask |= 1u << ((int)e / e_local);
             }
         }
-        for (int d = 0; d < N; ++d)
+        for (int d = 0; d < N; ++d) {
             if (mask >> d & 1u) atomicAdd(&sh[E + d], 1);
+            if (in_rank != nullptr) in_rank[(long)t * N + d] = (uint8_t)(mask >> d & 1u);   // is_token_in_rank of the layout API
+        }
         atomicAdd(&sh[E + N], __popc(mask));
         atomicAdd(&sh[E + N + 1], 1);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < C; i += blockDim.x) chunk_hist[(long)blockIdx.x * C + i] = sh[i];
+}
+
+// Column sums of the per-chunk histograms: the counts of get_dispatch_layout.
+__global__ void __launch_bounds__(256) route_sum_kernel(const int* chunk_hist, int num_chunks, int C, int* totals) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    int s = 0;
+    for (int ch = 0; ch < num_chunks; ++ch) s += chunk_hist[(long)ch * C + c];
+    totals[c] = s;
 }
 
 // One block.  chunk_base[chunk][c] = exclusive prefix over chunks; totals go to row `rank` of the
@@ -267,10 +278,15 @@ route_assign_kernel(const void* topk_idx, int is64, int T, int K, int E, int N, 
 
 int route_chunk_tokens() { return kChunkTokens; }
 
-cudaError_t route_hist(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, cudaStream_t stream) {
+cudaError_t route_hist(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, uint8_t* in_rank, cudaStream_t stream) {
     const int chunks = (T + kChunkTokens - 1) / kChunkTokens;
     if (chunks == 0) return cudaSuccess;
-    route_hist_kernel<<<chunks, kChunkTokens, (E + N + 2) * sizeof(int), stream>>>(topk_idx, is64, T, K, E, N, chunk_hist);
+    route_hist_kernel<<<chunks, kChunkTokens, (E + N + 2) * sizeof(int), stream>>>(topk_idx, is64, T, K, E, N, chunk_hist, in_rank);
+    return cudaGetLastError();
+}
+
+cudaError_t route_sum(const int* chunk_hist, int num_chunks, int C, int* totals, cudaStream_t stream) {
+    route_sum_kernel<<<(C + 255) / 256, 256, 0, stream>>>(chunk_hist, num_chunks, C, totals);
     return cudaGetLastError();
 }
 

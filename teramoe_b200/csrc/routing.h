@@ -21,7 +21,10 @@ struct LayoutOut {
 
 int route_chunk_tokens();
 
-cudaError_t route_hist(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, cudaStream_t stream);
+// in_rank (optional): [T, N] bytes, 1 where the token has an expert on that rank (is_token_in_rank of the layout API).
+cudaError_t route_hist(const void* topk_idx, int is64, int T, int K, int E, int N, int* chunk_hist, uint8_t* in_rank, cudaStream_t stream);
+// totals[c] = sum over chunks of chunk_hist[chunk][c]
+cudaError_t route_sum(const int* chunk_hist, int num_chunks, int C, int* totals, cudaStream_t stream);
 cudaError_t route_scan(const int* chunk_hist, int* chunk_base, int num_chunks, int E, int rank, int N, const uint64_t* meta_ptrs,
                        const uint64_t* signal_ptrs, int epoch, int* status, cudaStream_t stream);
 // cap_*: capacities (rows, padded slots, tokens; maxima over ranks) of tables that were sized before the layout was known;

@@ -70,7 +70,7 @@ def use_fused_combine(I: int, num_ranks: int, backward: bool) -> bool:
 OVERLAP_BWD_COMBINE = os.environ.get("TERAMOE_OVERLAP_BWD_COMBINE", "0") == "1"
 OVERLAP_COMM_SMS = int(os.environ.get("TERAMOE_OVERLAP_COMM_SMS", "8"))
 
-TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw")
+TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw", "row_topk_idx", "row_topk_w")
 EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operand rows, first slot of every received row
 
 # Dispatch fused into the GEMM that consumes it (csrc/fused.cu): one cooperative kernel, a few CTA pairs
@@ -175,7 +175,7 @@ def _table_sizes(maxima, H: int, K: int):
     sizes = {
         "recv_x": rmax * H * 2, "slot_row": smax * 4, "slot_w": smax * 4, "slot_tk": smax * 4,
         "row_tok": rmax * 4, "row_land": rmax * 4, "row_slots": rmax * K * 4,
-        "landing": lmax * H * 2, "gtw": tmax * K * 4,
+        "landing": lmax * H * 2, "gtw": tmax * K * 4, "row_topk_idx": rmax * K * 8, "row_topk_w": rmax * K * 4,
         "slot_x": smax * H * 2, "row_first": rmax * 4,
     }
     return sizes, (rmax, smax, lmax, tmax)
@@ -256,13 +256,16 @@ class EPEngine:
                 "row_slots": v(offs["row_slots"], [rmax, K], torch.int32),
                 "landing": v(offs["landing"], [lmax, H], torch.bfloat16),
                 "gtw": v(offs["gtw"], [tmax * K], torch.float32),
+                "row_topk_idx": v(offs["row_topk_idx"], [rmax, K], torch.int64),
+                "row_topk_w": v(offs["row_topk_w"], [rmax, K], torch.float32),
                 **({"slot_x": v(offs["slot_x"], [smax, H], torch.bfloat16),
                     "row_first": v(offs["row_first"], [rmax], torch.int32)} if "slot_x" in offs else {}),
             }
         t = w.cpu_tables
         shapes = {"recv_x": ((rmax, H), dtype), "slot_row": ((smax,), torch.int32), "slot_w": ((smax,), torch.float32),
                   "slot_tk": ((smax,), torch.int32), "row_tok": ((rmax,), torch.int32), "row_land": ((rmax,), torch.int32),
-                  "row_slots": ((rmax, K), torch.int32), "landing": ((lmax, H), dtype), "gtw": ((tmax * K,), torch.float32)}
+                  "row_slots": ((rmax, K), torch.int32), "landing": ((lmax, H), dtype), "gtw": ((tmax * K,), torch.float32),
+                  "row_topk_idx": ((rmax, K), torch.int64), "row_topk_w": ((rmax, K), torch.float32)}
         for name, (shape, dt) in shapes.items():
             cur = t.get(name)
             if cur is None or tuple(cur.shape) != shape or cur.dtype != dt:
@@ -357,6 +360,10 @@ class EPEngine:
         if not ok:
             return False
         h.rows, h.slots, h.land_rows, h.maxima = R, S, Lr, (rmax, smax, lmax, tmax)
+        for name, n in (("slot_row", S), ("slot_w", S), ("slot_tk", S), ("row_slots", R), ("row_land", R), ("row_tok", R)):
+            t = getattr(h, name)
+            if t is not None and t.shape[0] > n:     # copies taken with the capacity of the tables: cut to the real sizes
+                setattr(h, name, t[:n])
         return True
 
     def _caps_key(self, h: LayerHandle):
@@ -387,17 +394,20 @@ class EPEngine:
             ext = self.ext
             if with_meta:
                 ext.slot_pad_fill(h.seg_offsets, h.expert_total_local, tabs["slot_row"], tabs["slot_w"], tabs["slot_tk"], h.mblock_expert,
-                                  h.unit_blk, h.num_units)
+                                  h.unit_blk, h.num_units, h.geom_ok if h.pending is not None else None)
             if T > 0:
                 tw = topk_weights if topk_weights is not None else torch.empty(T, K, dtype=torch.float32, device=x.device)
                 ext.dispatch_push(x, h.topk_idx, tw, E, N, h.send_slot, h.send_row, h.land_off,
-                                  w.ptr_table(w.data, 0, "data"), [offs[n] for n in TABLES], with_meta, 0)
+                                  w.ptr_table(w.data, 0, "data"), [offs[n] for n in TABLES], with_meta, 0,
+                                  h.geom_ok if h.pending is not None else None)
         else:
             if with_meta:
                 tabs["slot_row"].fill_(-1)
                 tabs["slot_w"].zero_()
                 tabs["slot_tk"].fill_(-1)
                 tabs["row_slots"].fill_(-1)
+                tabs["row_topk_idx"].fill_(-1)
+                tabs["row_topk_w"].zero_()
             yield ("push", _cpu_dispatch_writes(h, x, topk_weights, with_meta))
         self._mark("  dispatch push kernel")
         yield ("barrier",)
@@ -405,8 +415,9 @@ class EPEngine:
         return tabs, offs
 
     def snapshot_tables(self, h: LayerHandle, tabs) -> None:
-        """Copy this rank's receive tables out of the (shared, reused) arena into the handle."""
-        R, S = h.rows, h.slots
+        """Copy this rank's receive tables out of the (shared, reused) arena into the handle.  While the host has not
+        read the layout sizes (fixed-shape dispatch) the copies have the capacity of the tables."""
+        R, S = (h.maxima[0], h.maxima[1]) if h.pending is not None else (h.rows, h.slots)
         h.slot_row = tabs["slot_row"][:S].clone()
         h.slot_w = tabs["slot_w"][:S].clone()
         h.slot_tk = tabs["slot_tk"][:S].clone()
@@ -473,6 +484,8 @@ class EPEngine:
         """Un-fused combine of one row per received token (x [rows,H]); optionally carries the
         received top-k weights back to their source entries.  -> (combined_x [T,H], weights [T,K] | None)."""
         import copy
+        if not self.resolve_sizes(h):        # a handle of a fixed-shape dispatch: the sizes were copied long ago, this does not wait
+            raise RuntimeError("the dispatch received more rows than num_worst_tokens allows; its outputs are not valid")
         R, K, dev = h.rows, h.K, x.device
         if x.shape[0] < R:
             raise ValueError(f"expected {R} rows (one per received token), got {x.shape[0]}")
@@ -951,6 +964,9 @@ def _cpu_dispatch_writes(h: LayerHandle, x, topk_weights, with_meta):
             rs = torch.full((T, K), -1, dtype=torch.int32)
             rs[tt, pos[tt, kk]] = h.send_slot[tt, kk]
             wl.append(("row_slots", rows, rs[tok]))
+            here = (dst_k[tok] == d)
+            wl.append(("row_topk_idx", rows, torch.where(here, idx[tok] - d * El, torch.full_like(idx[tok], -1))))
+            wl.append(("row_topk_w", rows, torch.where(here, topk_weights[tok].float(), torch.zeros((), dtype=torch.float32))))
         writes[d] = wl
     return writes
 
