@@ -10,6 +10,7 @@
 #include "fused.h"
 #include "launch_count.h"
 #include "layer.h"
+#include "lowlat.h"
 #include "routing.h"
 #include "runtime.h"
 
@@ -376,10 +377,10 @@ int64_t moe_layer_max_work(bool bwd, int64_t max_units, int64_t H, int64_t I, in
 }
 
 void ep_barrier(torch::Tensor signal_ptrs, int64_t rank, int64_t N, int64_t epoch, c10::optional<torch::Tensor> status, int64_t site,
-                int64_t limit_ms, int64_t mode) {
+                int64_t limit_ms, int64_t mode, c10::optional<torch::Tensor> mask) {
     c10::cuda::CUDAGuard guard(signal_ptrs.device());
     TM_CHECK_CUDA(tmoe::ep_barrier(u64(signal_ptrs, "signal_ptrs"), (int)rank, (int)N, (int)epoch, opt_status(status), (int)site,
-                                   (int)limit_ms, (int)mode, cur_stream()));
+                                   (int)limit_ms, (int)mode, mask.has_value() ? i32(*mask, "mask") : nullptr, cur_stream()));
 }
 
 void dispatch_push(torch::Tensor x, torch::Tensor topk_idx, torch::Tensor topk_w, int64_t E, int64_t N, torch::Tensor send_slot,
@@ -474,6 +475,87 @@ torch::Tensor numerics_check(torch::Tensor a, torch::Tensor b) {
     return out;
 }
 
+// ---- low-latency kernels (lowlat.cu).  `geom` = [num_ranks, rank, num_experts, max_tokens, hidden, use_fp8, use_ue8m0, round_scale,
+// use_logfmt, off_d_stage, off_d_flags, off_c_stage, off_c_flags, d_msg_bytes, c_row_bytes]
+tmoe::LowLatLayout ll_layout(const std::vector<int64_t>& g) {
+    TORCH_CHECK(g.size() == 15, "low-latency geometry needs 15 numbers");
+    tmoe::LowLatLayout l{};
+    l.num_ranks = (int)g[0]; l.rank = (int)g[1]; l.num_experts = (int)g[2]; l.max_tokens = (int)g[3]; l.hidden = (int)g[4];
+    l.use_fp8 = (int)g[5]; l.use_ue8m0 = (int)g[6]; l.round_scale = (int)g[7]; l.use_logfmt = (int)g[8];
+    l.off_d_stage = (uint64_t)g[9]; l.off_d_flags = (uint64_t)g[10]; l.off_c_stage = (uint64_t)g[11]; l.off_c_flags = (uint64_t)g[12];
+    l.d_msg_bytes = (uint32_t)g[13]; l.c_row_bytes = (uint32_t)g[14];
+    return l;
+}
+int* opt_i32(const c10::optional<torch::Tensor>& t, const char* name) { return t.has_value() ? i32(*t, name) : nullptr; }
+long long* opt_i64(const c10::optional<torch::Tensor>& t, const char* name) {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt64 && t->is_contiguous(), name, " must be a contiguous int64 CUDA tensor");
+    return reinterpret_cast<long long*>(t->data_ptr<int64_t>());
+}
+
+void ll_dispatch_send(std::vector<int64_t> geom, torch::Tensor x, torch::Tensor topk_idx, torch::Tensor arena_ptrs, int64_t call_seq,
+                      c10::optional<torch::Tensor> mask) {
+    const TopK tk = topk(topk_idx);
+    const auto lay = ll_layout(geom);
+    TORCH_CHECK(x.dim() == 2 && x.size(0) == tk.T && x.size(1) == lay.hidden, "x must be [T, hidden]");
+    c10::cuda::CUDAGuard guard(x.device());
+    TM_CHECK_CUDA(tmoe::ll_dispatch_send(lay, bf16(x, "x"), tk.ptr, tk.is64, tk.T, tk.K, u64(arena_ptrs, "arena_ptrs"), call_seq,
+                                         opt_i32(mask, "mask"), cur_stream()));
+}
+
+void ll_dispatch_recv(std::vector<int64_t> geom, torch::Tensor arena_local, torch::Tensor recv_x, c10::optional<torch::Tensor> recv_scales,
+                      torch::Tensor src_info, torch::Tensor layout_range, torch::Tensor recv_count, c10::optional<torch::Tensor> expert_stats,
+                      c10::optional<torch::Tensor> wait_stats, int64_t call_seq, c10::optional<torch::Tensor> mask, bool shrink,
+                      int64_t limit_ms, c10::optional<torch::Tensor> status) {
+    const auto lay = ll_layout(geom);
+    const int El = lay.num_experts / lay.num_ranks;
+    const int64_t NM = (int64_t)lay.num_ranks * lay.max_tokens;
+    TORCH_CHECK(recv_x.is_cuda() && recv_x.is_contiguous() && recv_x.numel() == El * NM * lay.hidden, "recv_x must be [E_local, ranks*max_tokens, hidden]");
+    TORCH_CHECK(!lay.use_fp8 || (recv_scales.has_value() && recv_scales->is_cuda()), "FP8 dispatch needs a scales tensor");
+    TORCH_CHECK(src_info.numel() == El * NM && layout_range.numel() == El * lay.num_ranks && recv_count.numel() == El, "low-latency receive tensors");
+    c10::cuda::CUDAGuard guard(recv_x.device());
+    TM_CHECK_CUDA(tmoe::ll_dispatch_recv(lay, arena_local.data_ptr(), recv_x.data_ptr(), recv_scales.has_value() ? recv_scales->data_ptr() : nullptr,
+                                         i32(src_info, "src_info"), opt_i64(layout_range, "layout_range"), i32(recv_count, "recv_count"),
+                                         opt_i32(expert_stats, "expert_stats"), opt_i64(wait_stats, "wait_stats"), call_seq, opt_i32(mask, "mask"),
+                                         shrink ? 1 : 0, (uint64_t)limit_ms * 1000000ull, opt_status(status), cur_stream()));
+}
+
+void ll_combine_send(std::vector<int64_t> geom, torch::Tensor x, torch::Tensor src_info, torch::Tensor layout_range, torch::Tensor arena_ptrs,
+                     int64_t call_seq, c10::optional<torch::Tensor> mask) {
+    const auto lay = ll_layout(geom);
+    const int El = lay.num_experts / lay.num_ranks;
+    TORCH_CHECK(x.numel() == (int64_t)El * lay.num_ranks * lay.max_tokens * lay.hidden, "x must be [E_local, ranks*max_tokens, hidden]");
+    c10::cuda::CUDAGuard guard(x.device());
+    TM_CHECK_CUDA(tmoe::ll_combine_send(lay, bf16(x, "x"), i32(src_info, "src_info"), opt_i64(layout_range, "layout_range"),
+                                        u64(arena_ptrs, "arena_ptrs"), call_seq, opt_i32(mask, "mask"), cur_stream()));
+}
+
+void ll_combine_recv(std::vector<int64_t> geom, torch::Tensor arena_local, torch::Tensor topk_idx, torch::Tensor topk_weights, torch::Tensor out,
+                     c10::optional<torch::Tensor> wait_stats, int64_t call_seq, c10::optional<torch::Tensor> mask, bool shrink, int64_t limit_ms,
+                     c10::optional<torch::Tensor> status) {
+    const TopK tk = topk(topk_idx);
+    const auto lay = ll_layout(geom);
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == tk.T && out.size(1) == lay.hidden && topk_weights.numel() == (int64_t)tk.T * tk.K, "combine shapes");
+    c10::cuda::CUDAGuard guard(out.device());
+    TM_CHECK_CUDA(tmoe::ll_combine_recv(lay, arena_local.data_ptr(), tk.ptr, tk.is64, f32(topk_weights, "topk_weights"), tk.T, tk.K, bf16(out, "out"),
+                                        opt_i64(wait_stats, "wait_stats"), call_seq, opt_i32(mask, "mask"), shrink ? 1 : 0,
+                                        (uint64_t)limit_ms * 1000000ull, opt_status(status), cur_stream()));
+}
+
+void ll_mask_update(torch::Tensor mask, int64_t rank, int64_t value) {
+    c10::cuda::CUDAGuard guard(mask.device());
+    TM_CHECK_CUDA(tmoe::ll_mask_update(i32(mask, "mask"), (int)mask.numel(), (int)rank, (int)value, cur_stream()));
+}
+void ll_mask_query(torch::Tensor mask, torch::Tensor out) {
+    TORCH_CHECK(out.numel() >= mask.numel(), "mask_status too small");
+    c10::cuda::CUDAGuard guard(mask.device());
+    TM_CHECK_CUDA(tmoe::ll_mask_query(i32(mask, "mask"), (int)mask.numel(), i32(out, "mask_status"), cur_stream()));
+}
+void ll_mask_clean(torch::Tensor mask) {
+    c10::cuda::CUDAGuard guard(mask.device());
+    TM_CHECK_CUDA(tmoe::ll_mask_clean(i32(mask, "mask"), (int)mask.numel(), cur_stream()));
+}
+
 // Tensor view over a range of the local arena.
 torch::Tensor arena_view(tmoe::SymmetricArena& arena, int64_t offset, std::vector<int64_t> sizes, py::object dtype) {
     const auto st = torch::python::detail::py_object_to_dtype(dtype);
@@ -507,7 +589,7 @@ void register_more(pybind11::module_& m) {
     m.def("moe_layer_max_work", &moe_layer_max_work);
     m.def("moe_layer_schedule", &moe_layer_schedule);
     m.def("ep_barrier", &ep_barrier, py::arg("signal_ptrs"), py::arg("rank"), py::arg("N"), py::arg("epoch"), py::arg("status"),
-          py::arg("site"), py::arg("limit_ms"), py::arg("mode") = 0);
+          py::arg("site"), py::arg("limit_ms"), py::arg("mode") = 0, py::arg("mask") = py::none());
     m.def("dispatch_push", &dispatch_push, py::arg("x"), py::arg("topk_idx"), py::arg("topk_w"), py::arg("E"), py::arg("N"), py::arg("send_slot"),
           py::arg("send_row"), py::arg("land_off"), py::arg("arena_ptrs"), py::arg("offsets"), py::arg("with_meta"), py::arg("num_blocks"),
           py::arg("ok") = py::none());
@@ -519,6 +601,13 @@ void register_more(pybind11::module_& m) {
     m.def("slot_rows_push", &slot_rows_push);
     m.def("droute_push", &droute_push);
     m.def("numerics_check", &numerics_check);
+    m.def("ll_dispatch_send", &ll_dispatch_send);
+    m.def("ll_dispatch_recv", &ll_dispatch_recv);
+    m.def("ll_combine_send", &ll_combine_send);
+    m.def("ll_combine_recv", &ll_combine_recv);
+    m.def("ll_mask_update", &ll_mask_update);
+    m.def("ll_mask_query", &ll_mask_query);
+    m.def("ll_mask_clean", &ll_mask_clean);
 
     py::class_<tmoe::SymmetricArena>(m, "SymmetricArena")
         .def(py::init<int, int, size_t>(), py::arg("rank"), py::arg("world"), py::arg("bytes"))

@@ -28,9 +28,10 @@ namespace {
 
 // mode 0: signal every rank, then wait for every rank (a barrier); 1: signal only; 2: wait only.
 __global__ void ep_barrier_kernel(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, uint64_t limit_ns,
-                                  int mode) {
+                                  int mode, const int* mask) {
     __threadfence_system();
-    if ((int)threadIdx.x < N) {
+    // ranks marked in `mask` (elastic shrink) are neither signalled nor waited for
+    if ((int)threadIdx.x < N && (mask == nullptr || mask[threadIdx.x] == 0)) {
         if (mode != 2) {
             int* peer_sig = reinterpret_cast<int*>(signal_ptrs[threadIdx.x]);
             st_release_sys(peer_sig + rank, epoch);
@@ -375,9 +376,9 @@ int grid_for_warps(long warps, int block) {
 }  // namespace
 
 cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms, int mode,
-                       cudaStream_t stream) {
+                       const int* mask, cudaStream_t stream) {
     const uint64_t limit_ns = limit_ms > 0 ? (uint64_t)limit_ms * 1000000ull : 0ull;   // 0: the status block's run-time limit
-    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns, mode);
+    ep_barrier_kernel<<<1, 32 * ((N + 31) / 32), 0, stream>>>(signal_ptrs, rank, N, epoch, status, site, limit_ns, mode, mask);
     return cudaGetLastError();
 }
 

@@ -23,8 +23,9 @@ struct SymOffsets {
 // limit_ms <= 0 selects the run-time limit of the status block (ptx.cuh).
 // mode 0: barrier (signal every rank, wait for every rank); 1: signal only (never waits); 2: wait only.
 // The signal-only / wait-only forms on a second flag row are the release / acquire of the data arena between calls.
+// mask (optional, int[N] on the device): ranks with a non-zero entry are neither signalled nor waited for.
 cudaError_t ep_barrier(const uint64_t* signal_ptrs, int rank, int N, int epoch, int* status, int site, int limit_ms, int mode,
-                       cudaStream_t stream);
+                       const int* mask, cudaStream_t stream);
 
 cudaError_t dispatch_push(const void* x, const void* topk_idx, int is64, const float* topk_w, int T, int K, int H, int E, int N,
                           const int* send_slot, const int* send_row, const int* land_off, const uint64_t* arena_ptrs,

@@ -243,6 +243,7 @@ class EPEngine:
     # ------------------------------------------------------------------ table access
     def _tables(self, offs, maxima, H, K, dtype):
         w = self.world
+        w.arena_user = "tables"
         rmax, smax, lmax, tmax = maxima
         if self.is_cuda:
             v = w.data.view

@@ -52,6 +52,7 @@ class EPWorld:
         self._ptr_cache: Dict[str, torch.Tensor] = {}
         self.cpu_tables: Dict[str, torch.Tensor] = {}
         self.closed = False
+        self.wait_limit_ms = 30_000          # what kernels use when the status block holds no limit (csrc/ptx.cuh)
         if self.is_cuda:
             from .._build import load_ext
             self.ext = load_ext()
@@ -71,6 +72,7 @@ class EPWorld:
             if ms > 0:
                 self.set_wait_limit_ms(ms)
         self.strict_status = STRICT_STATUS
+        self.arena_user = None               # who laid the data arena out last (the low-latency windows keep flags there)
         self._release_seq = 0            # calls whose arena reads this rank has released (same on all ranks at the same call)
 
     # ------------------------------------------------------------------ construction
@@ -150,6 +152,7 @@ class EPWorld:
         """Limit of every device-side wait on ANOTHER rank (barriers, arrival counters), in milliseconds; 0 restores
         the built-in default (30 s; the reference budgets about 100 s, csrc/kernels/configs.cuh:20-26).  Waits inside
         one CTA pair keep their fixed 2 s."""
+        self.wait_limit_ms = int(ms) if ms > 0 else 30_000
         if self.is_cuda:
             self.status[4:6].view(torch.int64).fill_(int(ms) * 1_000_000)
 
@@ -221,13 +224,14 @@ class EPWorld:
         self.ext.ep_barrier(self.ptr_table(self.control, self.free_offset, "control_free"), self.rank, self.size, self._release_seq,
                             self.status, 560, 0, 2)
 
-    def device_barrier(self, site: int = 500, limit_ms: int = 0) -> None:
-        """Bounded all-rank barrier kernel on the current stream (limit_ms <= 0: the default 2 s)."""
+    def device_barrier(self, site: int = 500, limit_ms: int = 0, mask: Optional[torch.Tensor] = None) -> None:
+        """Bounded all-rank barrier kernel on the current stream (limit_ms <= 0: the run-time limit for waits on other
+        ranks).  `mask`: device int[ranks]; ranks marked there are neither signalled nor waited for."""
         if self.size == 1:
             return
         ep = self.next_epoch()
         self.ext.ep_barrier(self.ptr_table(self.control, self.signal_offset, "control_sig"), self.rank, self.size, ep,
-                            self.status, site, limit_ms)
+                            self.status, site, limit_ms, 0, mask)
 
     def drive(self, gen: Generator):
         """Run a pipeline generator to completion in real (one process per rank) mode."""
@@ -245,6 +249,10 @@ class EPWorld:
                     req = gen.send(None)
                 elif kind == "acquire":
                     self.acquire_arena()
+                    req = gen.send(None)
+                elif kind == "masked_barrier":
+                    if self.is_cuda:
+                        self.device_barrier(mask=req[1])
                     req = gen.send(None)
                 elif kind == "allgather":
                     t = req[1]

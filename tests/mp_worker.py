@@ -107,6 +107,143 @@ def main():
         for n in outs[0]:
             assert torch.equal(outs[0][n], outs[1][n]), f"{n} differs between runs"
         buf.destroy()
+    elif case == "soak":
+        # Buffer reuse under stress: routing re-drawn every step, two layers of different shapes interleaved on ONE buffer
+        # (fwd A, fwd B, bwd B, bwd A), a rank without tokens, ranks that exchange nothing, an arena that has to grow
+        # mid-run; every step the one-kernel path must equal the separate kernels bit for bit (slots are deterministic).
+        from teramoe_b200 import engine
+        steps = int(os.environ.get("SOAK_STEPS", "200"))
+        El = 2
+        E = El * world
+        shapes = {"A": (256, 512, 256, 4), "B": (192, 1024, 128, 2)}           # T, H, I, K
+        gw = torch.Generator().manual_seed(77)
+        weights = {}
+        for name, (T, H, I, K) in shapes.items():
+            Wg_all = (torch.randn(E, 2 * I, H, generator=gw) * 0.02).to(dtype)
+            Wd_all = (torch.randn(E, H, I, generator=gw) * 0.02).to(dtype)
+            weights[name] = (Wg_all[rank * El:(rank + 1) * El].to(dev), Wd_all[rank * El:(rank + 1) * El].to(dev))
+        buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True)
+
+        def draw(step, name):
+            T, H, I, K = shapes[name]
+            g = torch.Generator().manual_seed(1000 * step + 10 * rank + (1 if name == "B" else 0))
+            Tr = T if step % 7 != 3 else T * 3                                   # every seventh step is larger: the arena grows
+            if step % 5 == 2 and rank == world - 1:
+                Tr = 0                                                           # a rank without tokens
+            x = (torch.randn(Tr, H, generator=g) * 0.1).to(dtype).to(dev)
+            logits = torch.randn(Tr, E, generator=g)
+            if step % 4 == 1:
+                logits[:, : rank * El] = -1e9                                    # only own and higher ranks: some pairs exchange nothing
+            top = torch.topk(logits, K, dim=1)
+            idx = top.indices.to(torch.int64).to(dev)
+            if Tr > 3:
+                idx[2, 0] = -1
+            return x, idx, torch.softmax(top.values, dim=1).float().to(dev), (torch.randn(Tr, H, generator=g)).to(dtype).to(dev)
+
+        def run_pair(step):
+            """fwd A, fwd B, bwd B, bwd A -> all outputs and gradients"""
+            res, live = {}, {}
+            for name in ("A", "B"):
+                x, idx, w, go = draw(step, name)
+                Wg, Wd = weights[name]
+                leaves = [x.clone().requires_grad_(True), w.clone().requires_grad_(True), Wg.clone().requires_grad_(True),
+                          Wd.clone().requires_grad_(True)]
+                out = buf.teramoe_autograd(leaves[0], idx, leaves[1], leaves[2], leaves[3], E)
+                live[name] = (out, go, leaves)
+            for name in ("B", "A"):
+                out, go, leaves = live[name]
+                out.backward(go)
+                res[name] = [out.detach()] + [t.grad for t in leaves]
+            return res
+
+        for step in range(steps):
+            got = {}
+            for path in ("layer", "separate"):
+                engine._FUSED_DISPATCH_MODE = "1" if path == "layer" else "0"
+                engine._FUSED_MODE = "1" if path == "layer" else "0"
+                engine._LAYER_KERNEL_MODE = "1" if path == "layer" else "0"
+                got[path] = run_pair(step)
+            for name in ("A", "B"):
+                for i, (a, b) in enumerate(zip(got["layer"][name], got["separate"][name])):
+                    assert torch.equal(a, b), f"step {step} layer {name} tensor {i}: one-kernel path differs from the separate kernels"
+            if step % 50 == 0:
+                buf.check_status()
+        buf.check_status()
+        buf.destroy()
+    elif case == "cached_race":
+        # a cached-handle dispatch right behind another dispatch: the second call's rows must not land before the first
+        # call's result has been copied out, even when one rank's host is slow between the barrier and the copy
+        import time
+        T, H, E, K = 200, 512, 4 * world, 2
+        g = torch.Generator().manual_seed(31 + rank)
+        x1 = torch.randn(T, H, generator=g).to(dtype).to(dev)
+        x2 = x1 + 100
+        logits = torch.randn(T, E, generator=g)
+        top = torch.topk(logits, K, dim=1)
+        idx, w = top.indices.to(dev), torch.softmax(top.values, 1).to(dev)
+        buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True)
+        want, _, _, _, handle, _ = buf.deepep_dispatch(x1, topk_idx=idx, topk_weights=w, num_experts=E)
+        eng = buf._engine
+        orig = eng.dispatch_gen
+
+        def slow(*a, **k):
+            res = yield from orig(*a, **k)
+            if rank == 0:
+                time.sleep(0.3)                     # the copy of the received rows is enqueued late on this rank
+            return res
+        eng.dispatch_gen = slow
+        for _ in range(3):
+            r1, *_ = buf.deepep_dispatch(x1, handle=handle)
+            r2, *_ = buf.deepep_dispatch(x2, handle=handle)
+            torch.cuda.synchronize() if dev.type == "cuda" else None
+            assert torch.equal(r1, want), "rows of the next dispatch landed before the result was copied"
+            assert torch.equal(r2, want + 100)
+        buf.destroy()
+    elif case == "ll":
+        # low-latency kernels across ranks: bf16 and fp8 dispatch, weighted combine (plain and LogFMT-10)
+        from teramoe_b200.low_latency import fp8_dequantize
+        T, H, K, M = 60 + 5 * rank, 1024, 4, 96
+        El = 3
+        E = El * world
+        g = torch.Generator().manual_seed(500 + rank)
+        x = (torch.randn(T, H, generator=g) * 0.3).to(dtype).to(dev)
+        idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(dev)
+        idx[0, 1] = -1
+        w = torch.rand(T, K, generator=g).to(dev)
+        buf = tm.Buffer(group, int(1e6) // 128 * 128, low_latency_mode=True, explicitly_destroy=True)
+        xs = [torch.empty(60 + 5 * r, H, dtype=dtype, device=dev) for r in range(world)]
+        ids = [torch.empty(60 + 5 * r, K, dtype=idx.dtype, device=dev) for r in range(world)]
+        dist.all_gather(xs, x)
+        dist.all_gather(ids, idx)
+        for use_fp8 in (False, True):
+            stats = torch.zeros(El, dtype=torch.int32, device=dev)
+            waits = torch.zeros(world, dtype=torch.int64, device=dev)
+            recv, count, handle, _, _ = buf.low_latency_dispatch(x, idx, M, E, cumulative_local_expert_recv_stats=stats,
+                                                                 dispatch_wait_recv_cost_stats=waits, use_fp8=use_fp8)
+            torch.cuda.synchronize()
+            for le in range(El):
+                ge = rank * El + le
+                want = torch.cat([xs[s][(ids[s] == ge).any(1)] for s in range(world)])
+                assert count[le].item() == want.shape[0] == stats[le].item()
+                got = fp8_dequantize(recv[0][le, : want.shape[0]], recv[1][le, : want.shape[0]].contiguous(), torch.float32) if use_fp8 \
+                    else recv[le, : want.shape[0]].float()
+                lim = 0.07 * max(1.0, want.float().abs().max().item()) if use_fp8 else 0.0
+                assert (got - want.float()).abs().max().item() <= lim
+        recv, count, handle, _, _ = buf.low_latency_dispatch(x, idx, M, E, use_fp8=False)
+        y = torch.zeros_like(recv)
+        for le in range(El):
+            y[le] = (recv[le].float() * 0.25 * ((rank * El + le) % 5 + 1)).to(dtype)
+        for use_logfmt in (False, True):
+            out, _, _ = buf.low_latency_combine(y, idx, w, handle, use_logfmt=use_logfmt)
+            want = torch.zeros(T, H, dtype=torch.float32, device=dev)
+            for k in range(K):
+                e = idx[:, k]
+                rows = (x.float() * 0.25 * ((e.clamp(min=0) % 5).float() + 1)[:, None]).to(dtype).float()
+                want += torch.where((e >= 0)[:, None], w[:, k:k + 1] * rows, torch.zeros((), device=dev))
+            tol = 3e-2 if use_logfmt else 1e-2
+            assert (out.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+        buf.check_status()
+        buf.destroy()
     elif case == "mismatch":
         # ranks disagree on num_experts: the host-side check must raise on every rank, nothing hangs
         buf = tm.Buffer(group, device=dev)

@@ -69,3 +69,28 @@ def test_nccl_layer_default_rules_pick_fused_kernels():
     world = torch.cuda.device_count()
     world = 8 if world >= 8 else 4 if world >= 4 else 2
     _launch("nccl", "layer_auto", world, timeout=600)
+
+
+def _world():
+    world = torch.cuda.device_count()
+    return 8 if world >= 8 else 4 if world >= 4 else 2
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_soak_changing_routing_interleaved_layers():
+    """Race / reuse soak (the reference's accuracy script repeats 10,000 identical steps,
+    tests/test_teramoe_accuracy.py:296-305; here every step is different): see the "soak" case of mp_worker.py."""
+    _launch("nccl", "soak", _world(), timeout=1500, extra_env={"SOAK_STEPS": os.environ.get("SOAK_STEPS", "200")})
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_cached_dispatch_behind_a_slow_rank():
+    _launch("nccl", "cached_race", _world(), timeout=300)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_low_latency_round_trip():
+    _launch("nccl", "ll", _world(), timeout=300)
