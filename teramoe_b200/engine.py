@@ -196,7 +196,7 @@ class EPEngine:
         self.is_cuda = world.is_cuda
         self.ext = world.ext if self.is_cuda else None
         self._trace = None          # list of (phase name, CUDA event) while tracing
-        self._caps = {}             # (T, K, E, N) -> (rows, slots, tokens) capacities learnt from earlier calls (layout_gen)
+        self._caps = {}             # (K, E, N) -> (rows, slots, tokens) capacities learnt from earlier calls (layout_gen)
         self.last_wait_ns = {}      # whole-layer kernel: {0: forward, 1: backward} -> int64[8] wait counters (csrc/layer.h LayerStat)
         self.last_paths = {}
 
@@ -368,7 +368,9 @@ class EPEngine:
         return True
 
     def _caps_key(self, h: LayerHandle):
-        return (h.T, h.K, h.E, h.N)
+        # only what every rank knows alike: the capacities decide the arena geometry, which must be the same on all ranks
+        # (a rank's own token count is NOT part of the key; the maxima over ranks that feed the capacities are global)
+        return (h.K, h.E, h.N)
 
     def _note_caps(self, h: LayerHandle, seen) -> None:
         """Capacities for the next call with the same shapes: what was seen plus a margin for the step-to-step change
@@ -573,7 +575,7 @@ class EPEngine:
         # Calls that will run as one kernel do not wait for the layout sizes: tables are sized by capacities learnt from
         # earlier calls with these shapes, and the sizes are read while the kernel runs (layout_gen, resolve_sizes).
         K0 = topk_idx.shape[1]
-        caps = self._caps.get((T, K0, num_experts, w.size)) if (self.is_cuda and use_layer_kernel() and LAUNCH_AHEAD) else None
+        caps = self._caps.get((K0, num_experts, w.size)) if (self.is_cuda and use_layer_kernel() and LAUNCH_AHEAD) else None
         h = yield from self.layout_gen(topk_idx, num_experts, caps=caps)
         self._mark("fwd:routing+layout")
         h.topk_weights = topk_weights
@@ -808,9 +810,15 @@ class EPEngine:
         # per-role wait times of this launch (ns summed over waiting threads), kept on the device until somebody asks
         wait_ns = torch.zeros(24, dtype=torch.int64, device=dev)
         self.last_wait_ns[kind] = wait_ns
-        ext.moe_layer(bwd, gemm_t, layout, send_t, sym_t, offsets, push_t, red_t, work_t, E, N, h.rank, w.next_epoch(),
-                      dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns,
-                      saved.saved_x if (bwd and S > 0) else None, ok)
+        epoch = w.next_epoch()
+        if ahead and T > h.maxima[3]:
+            # more tokens here than the tables were sized for: the device flag is 0 on EVERY rank (the maximum over ranks
+            # exceeds the capacity), so their kernels return at once; nothing to launch, the call is repeated below
+            pass
+        else:
+            ext.moe_layer(bwd, gemm_t, layout, send_t, sym_t, offsets, push_t, red_t, work_t, E, N, h.rank, epoch,
+                          dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns,
+                          saved.saved_x if (bwd and S > 0) else None, ok)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         if bwd:

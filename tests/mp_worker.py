@@ -110,7 +110,9 @@ def main():
     elif case == "soak":
         # Buffer reuse under stress: routing re-drawn every step, two layers of different shapes interleaved on ONE buffer
         # (fwd A, fwd B, bwd B, bwd A), a rank without tokens, ranks that exchange nothing, an arena that has to grow
-        # mid-run; every step the one-kernel path must equal the separate kernels bit for bit (slots are deterministic).
+        # mid-run.  Every step the one-kernel path must equal the two-kernel fused path bit for bit (same slots, same tiles,
+        # same order of the sums) and the separate kernels within bf16 tolerance (they round once more: a token's rows of
+        # one rank are summed there before they travel).
         from teramoe_b200 import engine
         steps = int(os.environ.get("SOAK_STEPS", "200"))
         El = 2
@@ -158,14 +160,19 @@ def main():
 
         for step in range(steps):
             got = {}
-            for path in ("layer", "separate"):
-                engine._FUSED_DISPATCH_MODE = "1" if path == "layer" else "0"
-                engine._FUSED_MODE = "1" if path == "layer" else "0"
+            for path in ("layer", "fused") + (("separate",) if step % 10 == 0 else ()):
+                engine._FUSED_DISPATCH_MODE = "0" if path == "separate" else "1"
+                engine._FUSED_MODE = "0" if path == "separate" else "1"
                 engine._LAYER_KERNEL_MODE = "1" if path == "layer" else "0"
                 got[path] = run_pair(step)
             for name in ("A", "B"):
-                for i, (a, b) in enumerate(zip(got["layer"][name], got["separate"][name])):
-                    assert torch.equal(a, b), f"step {step} layer {name} tensor {i}: one-kernel path differs from the separate kernels"
+                for i, (a, b) in enumerate(zip(got["layer"][name], got["fused"][name])):
+                    assert torch.equal(a, b), f"step {step} layer {name} tensor {i}: one-kernel path differs from the two-kernel fused path"
+                if "separate" in got:
+                    for i, (a, b) in enumerate(zip(got["layer"][name], got["separate"][name])):
+                        if a.numel():
+                            err = (a.float() - b.float()).abs().max().item()
+                            assert err <= 2e-2 * max(1.0, b.float().abs().max().item()), f"step {step} layer {name} tensor {i}: {err}"
             if step % 50 == 0:
                 buf.check_status()
         buf.check_status()
