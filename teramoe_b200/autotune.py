@@ -1,4 +1,7 @@
-"""Grid search over (compute_batch_size, combine_start_head_percent).
+"""Grid search over (compute_batch_size, combine_start_head_percent), the two arguments that shape the work list of the
+whole-layer kernel (batch size of the schedule; how far the first GEMM runs ahead of the second GEMM + combine push).
+`num_dispatch_sms` and `stage` can be swept as well (`dispatch_sms_list`, `stages`); the best of them is recorded in the
+result's `extra`.
 
 Same signature and return value as the reference (teramoe/autotune.py:59-177): returns
 (AutotuneResult, [(compute_batch_size, percent, ms), ...]).  Differences: the timed region can be
@@ -25,6 +28,7 @@ class AutotuneResult:
     time_ms: float
     forward_ms: Optional[float] = None
     backward_ms: Optional[float] = None
+    extra: Optional[dict] = None          # {"num_dispatch_sms": ..., "stage": ...} of the best configuration when those were swept
 
 
 def _barrier(group):
@@ -43,7 +47,8 @@ def _max_over_ranks(v: float, group, device) -> float:
 def autotune_teramoe(buffer, x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms: int = 24,
                      num_combine_sms: int = 24, total_sms: int = 148, stage: int = 1, num_iters: int = 1000, warmup_iters: int = 10,
                      verbose: bool = True, group: Optional[dist.ProcessGroup] = None, mode: str = "fwd",
-                     compute_batch_sizes=None, combine_start_head_percents=None) -> Tuple[AutotuneResult, List[Tuple[int, int, float]]]:
+                     compute_batch_sizes=None, combine_start_head_percents=None, dispatch_sms_list=None,
+                     stages=None) -> Tuple[AutotuneResult, List[Tuple[int, int, float]]]:
     if mode not in ("fwd", "fwd_bwd"):
         raise ValueError("mode must be 'fwd' or 'fwd_bwd'")
     group = group if group is not None else buffer.group
@@ -57,8 +62,11 @@ def autotune_teramoe(buffer, x, topk_idx, topk_weights, W_gateup, W_down, num_ex
     if mode == "fwd_bwd":
         leaves = [t.detach().requires_grad_(True) for t in (x, topk_weights, W_gateup, W_down)]
 
+    extra_grid = list(itertools.product(list(dispatch_sms_list or [num_dispatch_sms]), list(stages or [stage])))
+    cur = {"num_dispatch_sms": num_dispatch_sms, "stage": stage}
+
     def step(cbs, pct):
-        kw = dict(num_dispatch_sms=num_dispatch_sms, num_combine_sms=num_combine_sms, total_sms=total_sms, stage=stage,
+        kw = dict(num_dispatch_sms=cur["num_dispatch_sms"], num_combine_sms=num_combine_sms, total_sms=total_sms, stage=cur["stage"],
                   compute_batch_size=cbs, combine_start_head_percent=pct)
         if mode == "fwd":
             buffer.teramoe_autograd(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, **kw)
@@ -69,7 +77,8 @@ def autotune_teramoe(buffer, x, topk_idx, topk_weights, W_gateup, W_down, num_ex
             for t in leaves:
                 t.grad = None
 
-    for cbs, pct in itertools.product(cbs_list, pct_list):
+    for (dsm, stg), (cbs, pct) in itertools.product(extra_grid, itertools.product(cbs_list, pct_list)):
+        cur["num_dispatch_sms"], cur["stage"] = dsm, stg
         _barrier(group)
         for _ in range(warmup_iters):
             step(cbs, pct)
@@ -93,9 +102,10 @@ def autotune_teramoe(buffer, x, topk_idx, topk_weights, W_gateup, W_down, num_ex
         ms = _max_over_ranks(ms, group, x.device)
         results.append((cbs, pct, ms))
         if verbose and buffer.rank == 0:
-            print(f"[autotune] compute_batch_size={cbs} combine_start_head_percent={pct}: {ms:.4f} ms", flush=True)
+            more = f" num_dispatch_sms={dsm} stage={stg}" if len(extra_grid) > 1 else ""
+            print(f"[autotune] compute_batch_size={cbs} combine_start_head_percent={pct}{more}: {ms:.4f} ms", flush=True)
         if best is None or ms < best.time_ms:
-            best = AutotuneResult(cbs, pct, ms)
+            best = AutotuneResult(cbs, pct, ms, extra=(dict(cur) if len(extra_grid) > 1 else None))
     if verbose and buffer.rank == 0 and best is not None:
         print(f"[autotune] best: compute_batch_size={best.compute_batch_size} "
               f"combine_start_head_percent={best.combine_start_head_percent} ({best.time_ms:.4f} ms)", flush=True)

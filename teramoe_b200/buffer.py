@@ -445,7 +445,21 @@ class Buffer(LowLatencyMixin):
         x [T,H] bf16; topk_idx [T,K] (global expert ids, -1 = none); topk_weights [T,K] fp32;
         W_gateup [E_local, 2I, H] with rows interleaved (g0,u0,g1,u1,...); W_down [E_local, H, I].
         Gradients flow to x, topk_weights, W_gateup, W_down.  `grad_topk_weights` may be a
-        preallocated fp32 [T,K] tensor that receives d(topk_weights)."""
+        preallocated fp32 [T,K] tensor that receives d(topk_weights).
+
+        What the schedule arguments do here (same names and accepted values as the reference, teramoe/buffer.py:764-790):
+          num_dispatch_sms            SMs (two per CTA pair) that first stream this rank's rows to the other ranks and then
+                                      join the GEMM work
+          total_sms                   grid of the layer kernel / the GEMM kernels
+          compute_batch_size          rows per batch of the work list (1024 / 2048 / 4096): a batch's second GEMM follows
+                                      its first GEMM batch by batch, so it sets how much activation sits between them
+          combine_start_head_percent  how far (percent of a batch) the first GEMM runs ahead before the batch's second
+                                      GEMM, whose epilogue is the combine push, is scheduled
+          stage                       how finely units are ordered by the arrival of their rows (1: four groups, 2: eight)
+          num_combine_sms             the separate kernels only (small shapes): SMs of the combine push kernel; in the
+                                      one-kernel path every worker's epilogue pushes, so there is nothing to set aside
+          dispatch_config / combine_config   accepted for compatibility (chunk sizes of rings that do not exist here)
+        `autotune_teramoe` sweeps compute_batch_size x combine_start_head_percent like the reference's tuner."""
         self._check_layer_args(x, topk_idx, topk_weights, W_gateup, W_down, num_experts, num_dispatch_sms, num_combine_sms, total_sms,
                                stage, compute_batch_size, combine_start_head_percent)
         opts = {"num_dispatch_sms": num_dispatch_sms, "num_combine_sms": num_combine_sms, "total_sms": total_sms, "stage": stage,

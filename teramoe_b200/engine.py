@@ -81,7 +81,7 @@ EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operan
 # Measured (H=7168, I=2048, top-8, 8192 tokens/rank, step ms fused / separate on the same box):
 # EP=1 16.0 / 16.5 and 16.3 / 17.0 (two boxes' clocks), EP=2 17.0 / 17.4, EP=4 17.2 / 17.4, EP=8 19.0 / 19.1.
 _FUSED_DISPATCH_MODE = os.environ.get("TERAMOE_FUSED_DISPATCH", "auto")
-FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "4e9")))
+FUSED_DISPATCH_MAX_BYTES = int(float(os.environ.get("TERAMOE_FUSED_DISPATCH_MAX_BYTES", "8e9")))
 # CTA pairs that dispatch before they join the GEMM: "n" or "forward,backward"
 # Unset: the layer's `num_dispatch_sms` argument decides (two SMs per pair), like the reference's dispatch-SM knob.
 _pairs_env = os.environ.get("TERAMOE_FUSED_DISPATCH_PAIRS")
@@ -99,6 +99,8 @@ FUSED_DISPATCH_GROUPS = int(os.environ.get("TERAMOE_FUSED_DISPATCH_GROUPS", "4")
 # The whole layer direction as ONE cooperative kernel (csrc/layer.cu): dispatch, both GEMMs, the combine push, the
 # weight gradients (backward) and the reduce run as items of one work list.  "auto": wherever the fused dispatch applies.
 _LAYER_KERNEL_MODE = os.environ.get("TERAMOE_LAYER_KERNEL", "auto")
+# NVTX marks at every phase boundary of the host path (TERAMOE_NVTX=1), for time lines taken with a system profiler.
+NVTX_MARKS = os.environ.get("TERAMOE_NVTX", "0") == "1"
 # Enqueue the whole forward before the host has read the layout sizes (see EPEngine.layout_gen); "0" waits for them first.
 LAUNCH_AHEAD = os.environ.get("TERAMOE_LAUNCH_AHEAD", "1") == "1"
 LAYER_REDUCE_CHUNK = 64          # tokens per reduce item
@@ -208,6 +210,8 @@ class EPEngine:
         self._trace = [] if (on and self.is_cuda) else None
 
     def _mark(self, name: str) -> None:
+        if NVTX_MARKS and self.is_cuda:
+            torch.cuda.nvtx.mark("teramoe " + name.strip())      # phase boundaries on the host time line of a profiler
         if self._trace is not None:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
@@ -470,10 +474,11 @@ class EPEngine:
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=device))
         return out, gtw
 
-    def combine_gen(self, h: LayerHandle, y: torch.Tensor, tabs, offs, droute_parts: Optional[torch.Tensor] = None):
+    def combine_gen(self, h: LayerHandle, y: torch.Tensor, tabs, offs, droute_parts: Optional[torch.Tensor] = None, num_sms: int = 0):
         """Sum each received token's local expert outputs and push one row back to its source; after
-        the barrier reduce the landed rows.  -> (out [T,H], gtw [T,K] or None)."""
-        writes = self._combine_push(h, y, offs, droute_parts)
+        the barrier reduce the landed rows.  -> (out [T,H], gtw [T,K] or None).  num_sms > 0 limits the push kernel to
+        eight blocks per SM on that many SMs (the layer call's num_combine_sms)."""
+        writes = self._combine_push(h, y, offs, droute_parts, num_blocks=8 * num_sms)
         if writes is not None:
             yield ("push", writes)
         self._mark("  combine push kernel")
@@ -648,7 +653,7 @@ class EPEngine:
             y = gemm.fwd_down(act, W_down, h.mblock_expert, h.num_mblocks, st, num_sms, units=units)
             del act
             self._mark("fwd:down GEMM")
-            out, _ = yield from self.combine_gen(h, y, tabs, offs)
+            out, _ = yield from self.combine_gen(h, y, tabs, offs, num_sms=int((impl or {}).get("num_combine_sms", 0)))
             del y
         self._mark("fwd:combine (rest)")
         saved = SavedForBackward(h, saved_x, preact, stats=self._stats(h, H)) if keep_for_backward else None
@@ -769,7 +774,10 @@ class EPEngine:
                               h.unit_blk, h.num_units, ok)
             h.unit_order = torch.zeros(h.unit_blk.numel(), **i32)
             blk_group = torch.zeros(max(S // 128, 1), **i32)
-            ext.arrival_order(w.meta_view(E + N + 2), h.rank, N, E, max(1, min(FUSED_DISPATCH_GROUPS, N)), h.seg_offsets, h.unit_blk,
+            # `stage` of the layer call: how finely units are ordered by the arrival time of their rows (stage 1: four
+            # groups, stage 2: eight; the reference's stage splits every channel's tokens into that many sub-ranges)
+            groups = FUSED_DISPATCH_GROUPS * max(1, int(opts.get("stage", 1)))
+            ext.arrival_order(w.meta_view(E + N + 2), h.rank, N, E, max(1, min(groups, N)), h.seg_offsets, h.unit_blk,
                               h.num_units, blk_group, h.unit_order, ok)
         ext.zero_pad_rows(h.seg_offsets, h.expert_total_local, tabs["slot_x"], ok)
         out0 = torch.empty(R, I, **bf)
@@ -939,7 +947,7 @@ class EPEngine:
             gtw = torch.where(valid, tabs["gtw"][:T * K].view(T, K), torch.zeros((), dtype=torch.float32, device=dx.device))
             self._mark("bwd:combine reduce (per-entry rows)")
             return dx, gtw, dW_gateup, dW_down
-        dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts)
+        dx, gtw = yield from self.combine_gen(h, dxperm, tabs, offs, droute_parts=parts, num_sms=int((impl or {}).get("num_combine_sms", 0)))
         self._mark("bwd:combine (rest)")
         return dx, gtw, dW_gateup, dW_down
 

@@ -164,3 +164,20 @@ def test_layer_kernel_zero_tokens_and_changing_routing(monkeypatch):
             assert_close_bf16(got[name].float(), ref[name].cuda().float(), f"step {step} {name}")
     buf.check_status()
     buf.destroy()
+
+
+def test_autotune_sweeps_the_schedule_knobs(monkeypatch):
+    """autotune_teramoe walks compute_batch_size x combine_start_head_percent (plus, on request, num_dispatch_sms and stage),
+    which shape the work list of the layer kernel; it returns the reference's structure."""
+    _set_path(monkeypatch, "layer")
+    prob = make_problem(1, 512, 512, 256, 8, 4, seed=3, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02)
+    r = prob["ranks"][0]
+    buf = tm.Buffer(None, int(64e6), explicitly_destroy=True)
+    best, results = tm.autotune_teramoe(buf, r["x"], r["idx"], r["w"], prob["W_gateup"], prob["W_down"], 8, num_iters=2, warmup_iters=1,
+                                        verbose=False, mode="fwd_bwd", compute_batch_sizes=[1024, 4096], combine_start_head_percents=[0, 100],
+                                        dispatch_sms_list=[8, 24], stages=[1, 2])
+    assert len(results) == 16 and best.time_ms == min(ms for _, _, ms in results)
+    assert best.compute_batch_size in (1024, 4096) and best.combine_start_head_percent in (0, 100)
+    assert best.extra["num_dispatch_sms"] in (8, 24) and best.extra["stage"] in (1, 2)
+    buf.check_status()
+    buf.destroy()
