@@ -1,0 +1,65 @@
+"""Host-side pieces that need no GPU: low-latency window geometry, capacity bookkeeping of the launch-ahead forward,
+CPU binding helper, Config invariants."""
+import os
+
+import pytest
+import torch
+
+from teramoe_b200.config import Config
+from teramoe_b200.engine import EPEngine, LayerHandle
+from teramoe_b200.low_latency import _ll_geometry
+from teramoe_b200.parallel.world import EPWorld
+from teramoe_b200.utils import numa
+
+
+@pytest.mark.parametrize("use_fp8,use_ue8m0,use_logfmt", [(False, False, False), (True, False, False), (True, True, True)])
+def test_low_latency_geometry_is_aligned_and_disjoint(use_fp8, use_ue8m0, use_logfmt):
+    N, E, M, H = 4, 32, 96, 1024
+    geom, total, flags = _ll_geometry(N, 1, E, M, H, use_fp8, use_ue8m0, use_ue8m0, use_logfmt)
+    off_d_stage, off_d_flags, off_c_stage, off_c_flags, d_msg, c_row = geom[9:15]
+    El, G = E // N, H // 128
+    assert d_msg % 16 == 0 and c_row % 16 == 0
+    assert d_msg >= 16 + ((H + (G if use_ue8m0 else 4 * G)) if use_fp8 else 2 * H)
+    assert c_row == (G * 272 if use_logfmt else 2 * H)
+    regions = [(off_d_stage, El * N * M * d_msg), (off_d_flags, El * N * 8), (off_c_stage, E * M * c_row), (off_c_flags, E * 8)]
+    for (a, n), (b, _) in zip(regions, regions[1:]):
+        assert a % 256 == 0 and a + n <= b
+    assert regions[-1][0] + regions[-1][1] <= total
+    assert flags == ((off_d_flags, El * N * 8), (off_c_flags, E * 8))
+
+
+def test_capacities_grow_only_and_do_not_depend_on_the_rank_token_count():
+    eng = EPEngine(EPWorld.single("cpu"))
+    mk = lambda T: LayerHandle(T, 8, 0, 64, 1, 0, 0, 0, 0, (0, 0, 0, 0), *([None] * 9))
+    eng._note_caps(mk(100), (1000, 2048, 100))
+    first = eng._caps[(8, 64, 1)]
+    assert first[0] >= 1000 and first[1] >= 2048 and first[1] % 128 == 0 and first[2] == 100
+    eng._note_caps(mk(7), (500, 1024, 300))          # another rank-local T, smaller rows: same key, capacities only grow
+    second = eng._caps[(8, 64, 1)]
+    assert second[0] == first[0] and second[1] == first[1] and second[2] == 300
+    assert eng._caps_key(mk(100)) == eng._caps_key(mk(7))
+
+
+def test_bind_to_gpu_without_nvml_changes_nothing(monkeypatch):
+    before = os.sched_getaffinity(0)
+    monkeypatch.setattr(numa, "gpu_cpu_affinity", lambda i: None)
+    assert numa.bind_to_gpu(0) is None
+    assert os.sched_getaffinity(0) == before
+    # with an affinity answer the process is restricted to the intersection with what it may use
+    some = sorted(before)[:1]
+    monkeypatch.setattr(numa, "gpu_cpu_affinity", lambda i: some + [10 ** 6])
+    assert numa.bind_to_gpu(0) == some
+    os.sched_setaffinity(0, before)
+    monkeypatch.setenv("TERAMOE_NO_BIND", "1")
+    assert numa.bind_to_gpu(0) is None
+
+
+def test_config_invariants_follow_the_reference():
+    c = Config(20, 6, 256, 6, 250)
+    assert c.num_max_rdma_chunked_recv_tokens == 252          # rounded up to whole send chunks (csrc/config.hpp:70)
+    with pytest.raises(ValueError):
+        Config(20, 256, 256, 6, 128)                          # nvl send chunk must be smaller than the receive chunk
+    with pytest.raises(ValueError):
+        Config(20, 6, 256, 100, 100)                          # rdma send chunk must be smaller than (and at most half of) the receive chunk
+    with pytest.raises(ValueError):
+        Config(-1)
