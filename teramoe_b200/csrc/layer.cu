@@ -790,6 +790,7 @@ struct ScheduleArgs {
 
 __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs a) {
     if (a.ok != nullptr && *a.ok == 0) return;
+    const int gtid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
     const int U = min(*a.num_units, a.max_units);
     const int SG = max(1, a.group_units);
     const int NG = (U + SG - 1) / SG;
@@ -815,7 +816,8 @@ __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs 
     const int lag_items = max((int)(((long)full1 * a.lag_percent + 99) / 100), a.min_lag_items);
     const int lg = max(1, (lag_items + full1 - 1) / full1);
     const int head_full = min(full1, max(0, lag_items - (lg - 1) * full1));
-    for (int g = 0; g < NG + lg && NG > 0; ++g) {
+    // blocks take the schedule's blocks in turn
+    for (int g = blockIdx.x; g < NG + lg && NG > 0; g += gridDim.x) {
         const int g2 = g - lg;                                     // batch whose second GEMM sits in this block
         // all batches but the last are full
         const int before1 = g < NG ? g * full1 : U * a.nb1;
@@ -834,14 +836,14 @@ __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs 
     int pos = U * (a.nb1 + a.nb2);
     if (a.bwd) {
         const int per_wd = a.mu_wd * a.nb_wd, per_wg = a.mu_wg * a.nb_wg;
-        for (int i = threadIdx.x; i < a.El * per_wd; i += blockDim.x) {
+        for (int i = gtid; i < a.El * per_wd; i += nthreads) {
             const int e = i / per_wd, r = i - e * per_wd;
             const int n_blk = r / a.mu_wd;
             const int k0 = a.seg_offsets[e], nk = (a.seg_offsets[e + 1] - k0) / BK;
             if (pos + i < a.max_work) a.work[pos + i] = make_int4(kWorkWgradDown | (e << 8), k0, n_blk | ((r - n_blk * a.mu_wd) << 16), nk);
         }
         pos += a.El * per_wd;
-        for (int i = threadIdx.x; i < a.El * per_wg; i += blockDim.x) {
+        for (int i = gtid; i < a.El * per_wg; i += nthreads) {
             const int e = i / per_wg, r = i - e * per_wg;
             const int n_blk = r / a.mu_wg;
             const int k0 = a.seg_offsets[e], nk = (a.seg_offsets[e + 1] - k0) / BK;
@@ -849,9 +851,9 @@ __global__ void __launch_bounds__(256) layer_schedule_kernel(const ScheduleArgs 
         }
         pos += a.El * per_wg;
     }
-    if (threadIdx.x == 0) *a.num_work = min(pos, a.max_work);
+    if (gtid == 0) *a.num_work = min(pos, a.max_work);
     // units are numbered expert by expert: first unit and unit count of every expert
-    for (int e = threadIdx.x; e < a.El; e += blockDim.x) {
+    for (int e = gtid; e < a.El; e += nthreads) {
         int first = 0;
         for (int j = 0; j < e; ++j) first += ((a.seg_offsets[j + 1] - a.seg_offsets[j]) / 128 + 1) / 2;
         a.expert_units[e] = make_int2(first, ((a.seg_offsets[e + 1] - a.seg_offsets[e]) / 128 + 1) / 2);
@@ -912,7 +914,7 @@ cudaError_t moe_layer_schedule(const LayerParams& p, cudaStream_t stream) {
     a.work = static_cast<int4*>(p.work); a.max_work = p.max_work; a.num_work = p.num_work;
     a.expert_units = reinterpret_cast<int2*>(p.expert_units);
     a.ok = p.geom_ok;
-    layer_schedule_kernel<<<1, 256, 0, stream>>>(a);
+    layer_schedule_kernel<<<32, 256, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -349,16 +349,37 @@ arrival_order_kernel(const int* meta, int rank, int N, int E, int groups, const 
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        const int nu = min(num_units_p[0], max_units);
-        int pos = 0;
-        for (int gsel = 0; gsel < groups; ++gsel)
-            for (int u = 0; u < nu; ++u) {
+    // units sorted by group, stable: one ordered compaction pass over the units per group (ballots + warp offsets)
+    __shared__ int warp_cnt[8];
+    __shared__ int base;
+    const int nu = min(num_units_p[0], max_units);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int gsel = 0; gsel < groups; ++gsel) {
+        for (int start = 0; start < nu; start += blockDim.x) {
+            const int u = start + threadIdx.x;
+            bool match = false;
+            if (u < nu) {
                 const int b = unit_blk[u];
                 int gu = blk_group[b];
                 if (unit_blk[u + 1] - b == 2) gu = max(gu, blk_group[b + 1]);
-                if (gu == gsel) unit_order[pos++] = u;
+                match = gu == gsel;
             }
+            const uint32_t bal = __ballot_sync(0xffffffffu, match);
+            if (lane == 0) warp_cnt[warp] = __popc(bal);
+            __syncthreads();
+            int off = base;
+            for (int w2 = 0; w2 < warp; ++w2) off += warp_cnt[w2];
+            if (match) unit_order[off + __popc(bal & ((1u << lane) - 1u))] = u;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int tot = 0;
+                for (int w2 = 0; w2 < (int)(blockDim.x >> 5); ++w2) tot += warp_cnt[w2];
+                base += tot;
+            }
+            __syncthreads();
+        }
     }
 }
 }  // namespace
