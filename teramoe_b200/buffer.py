@@ -17,7 +17,7 @@ from typing import Callable, List, Optional, Tuple, Union
 import torch
 import torch.distributed as dist
 
-from .config import Config, topk_idx_t
+from .config import COMPUTE_BATCH_SIZES, Config, topk_idx_t
 from .engine import EPEngine, LayerHandle
 from .low_latency import LowLatencyMixin
 from .parallel.world import EPWorld
@@ -416,7 +416,7 @@ class Buffer(LowLatencyMixin):
             raise ValueError("num_dispatch_sms and num_combine_sms must be even")
         if stage not in (1, 2):
             raise ValueError("stage must be 1 or 2")
-        if compute_batch_size not in (1024, 2048, 4096):
+        if compute_batch_size not in COMPUTE_BATCH_SIZES:
             raise ValueError("compute_batch_size must be one of 1024, 2048, 4096")
         if not 0 <= combine_start_head_percent <= 100:
             raise ValueError("combine_start_head_percent must be in [0, 100]")

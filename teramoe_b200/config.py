@@ -16,11 +16,13 @@ import torch
 # TOPK_IDX_BITS=32, csrc/kernels/configs.cuh:79-85; both widths are accepted at run time here).
 topk_idx_t = torch.int64
 
-# Role geometry of the fused kernels (csrc/config.hpp:8-32 in the reference).
-COMPUTE_GROUP_SIZE = 48
-COMPUTE_SCHEDULER_SMS = 1
-GATHER_SMS = 3
-COMPUTE_BATCH_SIZES = (1024, 2048, 4096)
+# Role geometry of the layer kernel (the reference's counterparts are the teramoe_config constants, csrc/config.hpp:8-32:
+# 48-SM compute groups, one scheduler SM, three gather SMs).  Here SMs are not partitioned by role: every CTA pair is a
+# worker on one work list, and the roles that run beside the workers are warps of every CTA.
+COMPUTE_BATCH_SIZES = (1024, 2048, 4096)     # accepted `compute_batch_size` values: rows per batch of the work list
+UNIT_ROWS = 256                              # rows of one unit (two 128-row blocks of one expert, one CTA pair)
+GATHER_WARPS_PER_CTA = 2                     # warps 2 and 3 of every CTA: reduce of landed rows, X expansion in backward
+EPILOGUE_WARPS_PER_CTA = 8
 
 
 @dataclass

@@ -20,6 +20,8 @@
 //
 // Reference counterpart: the optional MK_COMPUTE_KERNEL=2 path (csrc/teramoe/teramoe_wrapper.cuh:77-79,
 // :569, :655-659), which is not the reference's default.
+#include <cstdlib>
+
 #include "gemm.h"
 #include "gemm_common.cuh"
 
@@ -69,8 +71,13 @@ __device__ __forceinline__ bool get_tile2(const GemmArgs& g, int t, int num_unit
         if (t >= total) return false;
         tile.group = t / per_group;
         const int r = t - tile.group * per_group;
-        tile.n_blk = r / m_units;
-        tile.m_unit = r - tile.n_blk * m_units;
+        if (g.kgroup_n_fast) {
+            tile.m_unit = r / g.num_n_blocks;
+            tile.n_blk = r - tile.m_unit * g.num_n_blocks;
+        } else {
+            tile.n_blk = r / m_units;
+            tile.m_unit = r - tile.n_blk * m_units;
+        }
         tile.blk0 = 0;
         tile.two = 1;
         const int s0 = g.seg_offsets[tile.group];
@@ -292,7 +299,13 @@ cudaError_t gemm2_mgroup(int kind, const void* a, const void* b, const GemmArgs&
     }
 }
 
-cudaError_t gemm2_wgrad(const void* a, const void* b, const GemmArgs& g, int rows, int M, int N, int num_sms, cudaStream_t stream) {
+cudaError_t gemm2_wgrad(const void* a, const void* b, const GemmArgs& g_in, int rows, int M, int N, int num_sms, cudaStream_t stream) {
+    GemmArgs g = g_in;
+    {
+        // experiment switch: TMOE_WGRAD_ORDER=n / m forces the order in which consecutive tiles walk dW; default: row units first
+        static const char* env = getenv("TMOE_WGRAD_ORDER");
+        g.kgroup_n_fast = (env != nullptr && env[0] == 'n') ? 1 : 0;
+    }
     CUtensorMap ma, mb;
     cudaError_t e;
     if ((e = make_map(&ma, a, (uint64_t)rows, M, 64, BK)) != cudaSuccess) return e;

@@ -40,6 +40,7 @@ struct GemmArgs {
     int num_groups;              // K-grouped: number of experts
     const int* seg_offsets;      // K-grouped: [num_groups + 1] row offsets, multiples of 128
     int m_total;                 // K-grouped: rows of dW per expert
+    int kgroup_n_fast;           // K-grouped, CTA pairs: consecutive tiles walk the column blocks first (else the row units)
     __nv_bfloat16* d;            // main output
     int ldd;
     __nv_bfloat16* aux;          // preact (fwd gate_up) / dGU (bwd grad_act)

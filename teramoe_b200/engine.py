@@ -32,6 +32,7 @@ import torch
 
 from . import layout as L
 from .ops import gemm
+from .config import UNIT_ROWS
 from .parallel.world import EPWorld, _round_up
 
 # Feed the GEMMs through TMA row gather (tile::gather4) instead of an expanded slot-space copy.
@@ -809,7 +810,7 @@ class EPEngine:
                  w.ptr_table(w.control, w.signal_offset, "control_sig"), w.control.view(w.signal_offset, [N], torch.int32)]
         offsets = [offs["slot_x"], offs["slot_w"], offs["slot_tk"], offs["slot_row"], offs["row_first"], w.blk_cnt_offset,
                    offs["landing"], offs["gtw"]]
-        group_units = max(1, int(opts.get("compute_batch_size", 2048)) // 256)
+        group_units = max(1, int(opts.get("compute_batch_size", 2048)) // UNIT_ROWS)
         lag = int(opts.get("combine_start_head_percent", 70))
         # a second-GEMM item should find its unit's first GEMM finished, not merely claimed: keep it about two items per
         # CTA pair behind (TERAMOE_LAYER_MIN_LAG: items per pair)
