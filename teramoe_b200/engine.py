@@ -51,18 +51,31 @@ USE_CTA_PAIRS = os.environ.get("TERAMOE_CTA_PAIRS", "1") == "1"
 # 1.39 ms without, i.e. the all-to-all is hidden; the step drops from 17.3 to 16.8 ms.  (A first version
 # that stored 64-byte fragments straight from the epilogue registers cost +4 ms.)  "0" = separate
 # combine_push kernel (one row per (token, rank) on the wire instead of one per (token, k)).
-# The push is only hidden when the GEMM lasts longer than its transfer: per pushed byte the down GEMM
-# does I FLOPs and the dX GEMM 2I.  Measured with I=512 at EP=4 the pushed down GEMM took 4.1 ms (plain
-# GEMM 1.07 ms + separate push 1.29 ms) and the step 21.8 ms against 15.2 ms, so "auto" (the default)
-# fuses forward when I >= 1536 and backward when I >= 768, and always on a single rank.
+# The push is only hidden when the GEMM lasts longer than its transfer.  Per byte pushed over NVLink the down GEMM
+# does I FLOPs and the dX GEMM 2I (2*S*I*H resp. 2*S*2I*H FLOPs for S*H*2 bytes), and the machine balance is
+# WIRE_BALANCE = sustained GEMM rate / per-direction link rate = 1.4e15 / 770e9 = 1818 FLOP per byte.  The epilogue
+# push overlaps with the mainloop of the next tile, so the break-even sits a little below the balance: "auto" (the
+# default) fuses when FLOPs per byte >= FUSE_MIN_BALANCE * WIRE_BALANCE, i.e. forward I >= 1455, backward I >= 728,
+# and always on a single rank.  Checked against measurements: I=2048 wins fused at EP=2/4/8 (forward ratio 1.13),
+# I=512 loses (ratio 0.28: the pushed down GEMM took 4.1 ms against 1.07 ms GEMM + 1.29 ms separate push at EP=4, the
+# step 21.8 ms against 15.2 ms), I=14336 (ratio 7.9) wins.
 _FUSED_MODE = os.environ.get("TERAMOE_FUSED_COMBINE", "auto")
 FUSED_COMBINE = _FUSED_MODE != "0"
+SUSTAINED_GEMM_FLOPS = 1.4e15            # cuBLAS bf16 under the power cap on this part
+LINK_BYTES_PER_S = 770e9                 # measured peer copy, one direction
+WIRE_BALANCE = SUSTAINED_GEMM_FLOPS / LINK_BYTES_PER_S
+FUSE_MIN_BALANCE = float(os.environ.get("TERAMOE_FUSE_MIN_BALANCE", "0.8"))
+
+
+def flops_per_wire_byte(I: int, backward: bool) -> float:
+    """FLOPs of the GEMM whose epilogue pushes the combine rows, per byte it puts on the wire."""
+    return float(2 * I if backward else I)
 
 
 def use_fused_combine(I: int, num_ranks: int, backward: bool) -> bool:
     if _FUSED_MODE in ("0", "1"):
         return _FUSED_MODE == "1"
-    return num_ranks == 1 or I >= (768 if backward else 1536)
+    return num_ranks == 1 or flops_per_wire_byte(I, backward) >= FUSE_MIN_BALANCE * WIRE_BALANCE
 # Backward, more than one rank: the combine push of dX (+ barrier) can run on a side stream on a few SMs
 # while the two weight-gradient GEMMs, which nothing downstream waits for, run on the remaining SMs.
 # Measured at EP=2 (H=7168, I=2048): 18.0 ms per step with the overlap against 16.7 ms without (the
@@ -117,7 +130,8 @@ def use_fused_dispatch(I: int, num_ranks: int, table_bytes: int = 0) -> bool:
         return False
     if _FUSED_DISPATCH_MODE in ("0", "1"):
         return _FUSED_DISPATCH_MODE == "1"
-    return I >= 1536 and table_bytes <= FUSED_DISPATCH_MAX_BYTES
+    # same balance rule as the forward combine (the kernel needs the pushed combine, and its GEMM does 2I FLOPs per byte received)
+    return flops_per_wire_byte(I, False) >= FUSE_MIN_BALANCE * WIRE_BALANCE and table_bytes <= FUSED_DISPATCH_MAX_BYTES
 
 
 @dataclass

@@ -63,3 +63,18 @@ def test_config_invariants_follow_the_reference():
         Config(20, 6, 256, 100, 100)                          # rdma send chunk must be smaller than (and at most half of) the receive chunk
     with pytest.raises(ValueError):
         Config(-1)
+
+
+def test_fusion_rule_follows_flops_per_wire_byte():
+    """The combine is pushed from the GEMM epilogue only where the GEMM does enough FLOPs per byte it sends."""
+    from teramoe_b200 import engine as eng
+    if eng._FUSED_MODE != "auto" or eng._FUSED_DISPATCH_MODE != "auto":
+        pytest.skip("fusion forced by the environment")
+    assert eng.use_fused_combine(512, 1, False)                      # one rank: nothing crosses a link
+    assert not eng.use_fused_combine(512, 8, False) and not eng.use_fused_combine(512, 8, True)
+    assert eng.use_fused_combine(2048, 8, False) and eng.use_fused_combine(2048, 8, True)
+    assert eng.use_fused_combine(1024, 8, True) and not eng.use_fused_combine(1024, 8, False)   # dX does 2I per byte
+    assert eng.flops_per_wire_byte(2048, True) == 2 * eng.flops_per_wire_byte(2048, False)
+    if eng.USE_CTA_PAIRS and not eng.USE_TMA_GATHER:
+        assert eng.use_fused_dispatch(2048, 8, 0) and not eng.use_fused_dispatch(512, 8, 0)
+        assert not eng.use_fused_dispatch(2048, 8, eng.FUSED_DISPATCH_MAX_BYTES + 1)
