@@ -4,9 +4,11 @@ Reference counterparts: teramoe/buffer.py:32-147 (construction / destroy), :153-
 :293-454 (layout, dispatch, combine), :537-708 (low-latency API), :710-818 (fused autograd entry
 points).  Differences that matter to callers:
 
-* One NVSwitch node only (EP = 1, 2, 4, 8): `num_rdma_bytes`, `num_qps_per_rank`, `allow_mnnvl`,
-  `use_fabric` are accepted and ignored; the documented constructor call works on <= 8 ranks (the
-  reference rejects it there, csrc/moe_extension.cpp:161-162).
+* One NVSwitch node only (EP = 1, 2, 4, 8): `num_rdma_bytes`, `num_qps_per_rank`, `allow_mnnvl` are accepted and
+  ignored; the documented constructor call works on <= 8 ranks (the reference rejects it there,
+  csrc/moe_extension.cpp:161-162).
+* `use_fabric=True` allocates the symmetric arenas with the driver's virtual memory management (cuMemCreate, shared as
+  POSIX file descriptors; a fabric handle is requested too where the platform has one) instead of cudaMalloc + CUDA IPC.
 * `num_nvl_bytes` is a starting size: the symmetric arena grows (collectively) when a call needs more.
 * Slot assignment is deterministic, so results are bitwise reproducible run to run.
 """
@@ -103,7 +105,9 @@ class Buffer(LowLatencyMixin):
         self._destroyed = False
         if group is not None and self.device.type == "cuda":
             check_nvlink_connections(group)
-        self._world = EPWorld.from_group(group, self.device) if group is not None else EPWorld.single(self.device)
+        self.use_fabric = bool(use_fabric)
+        self._world = (EPWorld.from_group(group, self.device, use_fabric=self.use_fabric) if group is not None
+                       else EPWorld.single(self.device, use_fabric=self.use_fabric))
         self._engine = EPEngine(self._world)
         self._comm_stream = torch.cuda.Stream(self.device, priority=-1) if self.device.type == "cuda" else None
         if self.device.type == "cuda" and num_nvl_bytes > 0:

@@ -610,7 +610,12 @@ void register_more(pybind11::module_& m) {
     m.def("ll_mask_clean", &ll_mask_clean);
 
     py::class_<tmoe::SymmetricArena>(m, "SymmetricArena")
-        .def(py::init<int, int, size_t>(), py::arg("rank"), py::arg("world"), py::arg("bytes"))
+        .def(py::init<int, int, size_t, bool, bool>(), py::arg("rank"), py::arg("world"), py::arg("bytes"), py::arg("vmm") = false,
+             py::arg("fabric") = false)
+        .def("export_fd", &tmoe::SymmetricArena::export_fd)
+        .def("open_peer_fds", &tmoe::SymmetricArena::open_peer_fds)
+        .def("is_vmm", &tmoe::SymmetricArena::is_vmm)
+        .def("has_fabric_handle", &tmoe::SymmetricArena::has_fabric_handle)
         .def("export_handle", [](const tmoe::SymmetricArena& a) { return py::bytes(a.export_handle()); })
         .def("open_peers",
              [](tmoe::SymmetricArena& a, const std::vector<py::bytes>& hs) {

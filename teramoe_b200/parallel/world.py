@@ -3,7 +3,9 @@
 Three ways to run the same per-rank pipeline (teramoe_b200/engine.py):
 
 * ``EPWorld.from_group(group)``  one process per GPU; arenas are exchanged as CUDA IPC handles through
-  ``torch.distributed`` (NCCL or gloo is only the bootstrap, like teramoe/buffer.py:74-101).
+  ``torch.distributed`` (NCCL or gloo is only the bootstrap, like teramoe/buffer.py:74-101), or, with
+  ``use_fabric=True`` / ``TERAMOE_ARENA=vmm``, allocated with the driver's virtual memory management and shared as POSIX
+  file descriptors over Unix sockets (parallel/fdpass.py; reference: csrc/moe_extension.cpp:16-125).
   With CPU tensors the same class moves data with gloo collectives instead of peer stores.
 * ``EPWorld.single(device)``      one rank, no peers.
 * ``VirtualCluster(n, device)``   n ranks emulated in ONE process on ONE device (or on the CPU), stepped in
@@ -31,6 +33,8 @@ STRICT_STATUS = os.environ.get("TERAMOE_STRICT_STATUS", "0") == "1"
 CONTROL_ROW_INTS = 8192          # capacity of one metadata row (E + ranks + 2 ints must fit)
 MAX_BLOCKS = 65536               # per-block arrival counters of the fused dispatch (8.4 M slot rows)
 _ALIGN = 256
+# "ipc": cudaMalloc + CUDA IPC handles.  "vmm": cuMemCreate + shareable descriptors (what `use_fabric=True` selects).
+ARENA_KIND = os.environ.get("TERAMOE_ARENA", "ipc")
 
 
 def _round_up(v: int, a: int = _ALIGN) -> int:
@@ -40,9 +44,14 @@ def _round_up(v: int, a: int = _ALIGN) -> int:
 class EPWorld:
     """One rank's view of the expert-parallel group."""
 
-    def __init__(self, rank: int, size: int, device: torch.device, group=None, virtual_peers: Optional[list] = None):
+    def __init__(self, rank: int, size: int, device: torch.device, group=None, virtual_peers: Optional[list] = None,
+                 use_fabric: bool = False):
         self.rank, self.size, self.device = rank, size, torch.device(device)
         self.group = group
+        if ARENA_KIND not in ("ipc", "vmm"):
+            raise ValueError(f"TERAMOE_ARENA must be 'ipc' or 'vmm', not {ARENA_KIND!r}")
+        self.use_fabric = bool(use_fabric)
+        self.arena_vmm = (self.use_fabric or ARENA_KIND == "vmm") and virtual_peers is None
         self.virtual_peers = virtual_peers          # list of EPWorld in a VirtualCluster
         self.is_cuda = self.device.type == "cuda"
         self.epoch = 0
@@ -60,8 +69,7 @@ class EPWorld:
             self.free_offset = self.signal_offset + 512           # arena-release flags, one int per rank
             self.blk_cnt_offset = self.signal_offset + 1024
             self.control_bytes = _round_up(self.blk_cnt_offset + MAX_BLOCKS * 4 + 4096)
-            with torch.cuda.device(self.device):
-                self.control = self.ext.SymmetricArena(rank, size, self.control_bytes)
+            self.control = self._new_arena(self.control_bytes)
             # status block (csrc/ptx.cuh): words 0-3 error record, words 4-5 the limit (ns) of waits on other ranks
             self.status = torch.zeros(8, dtype=torch.int32, device=self.device)
             self.sizes_host = torch.zeros(12, dtype=torch.int32).pin_memory()
@@ -77,23 +85,35 @@ class EPWorld:
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def single(cls, device) -> "EPWorld":
-        w = cls(0, 1, device)
+    def single(cls, device, use_fabric: bool = False) -> "EPWorld":
+        w = cls(0, 1, device, use_fabric=use_fabric)
         if w.is_cuda:
             w.control.adopt_peer_pointers([w.control.local_ptr()])
         return w
 
     @classmethod
-    def from_group(cls, group, device) -> "EPWorld":
+    def from_group(cls, group, device, use_fabric: bool = False) -> "EPWorld":
         rank, size = dist.get_rank(group), dist.get_world_size(group)
-        w = cls(rank, size, device, group=group)
+        w = cls(rank, size, device, group=group, use_fabric=use_fabric)
         if w.is_cuda:
             w._open_ipc(w.control)
         return w
 
+    def _new_arena(self, nbytes: int):
+        with torch.cuda.device(self.device):
+            if self.arena_vmm:
+                return self.ext.SymmetricArena(self.rank, self.size, nbytes, vmm=True, fabric=self.use_fabric)
+            return self.ext.SymmetricArena(self.rank, self.size, nbytes)
+
     def _open_ipc(self, arena) -> None:
+        """Map every peer's arena (collective)."""
         if self.size == 1:
             arena.adopt_peer_pointers([arena.local_ptr()])
+            return
+        if arena.is_vmm():
+            from .fdpass import exchange_fds
+            with torch.cuda.device(self.device):
+                arena.open_peer_fds(exchange_fds(arena.export_fd(), self.rank, self.size, group=self.group))
             return
         handles: List[Optional[bytes]] = [None] * self.size
         dist.all_gather_object(handles, bytes(arena.export_handle()), group=self.group)
@@ -127,8 +147,7 @@ class EPWorld:
         if self.group is not None and self.size > 1:
             dist.barrier(group=self.group)
         old = self.data
-        with torch.cuda.device(self.device):
-            self.data = self.ext.SymmetricArena(self.rank, self.size, new_bytes)
+        self.data = self._new_arena(new_bytes)
         self._open_ipc(self.data)
         if old is not None:
             if self.group is not None and self.size > 1:

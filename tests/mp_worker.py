@@ -251,6 +251,60 @@ def main():
             assert (out.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
         buf.check_status()
         buf.destroy()
+    elif case == "fdpass":
+        # descriptors between processes: every rank offers an anonymous memory file that names it, twice in a row
+        from teramoe_b200.parallel.fdpass import exchange_fds
+        for rnd in range(2):
+            fd = os.memfd_create(f"rank{rank}")
+            os.write(fd, f"rank {rank} round {rnd}".encode())
+            fds = exchange_fds(fd, rank, world, group=group)
+            assert len(fds) == world and fds[rank] == fd
+            for r, f in enumerate(fds):
+                assert f >= 0
+                os.lseek(f, 0, os.SEEK_SET)
+                assert os.read(f, 64).decode() == f"rank {r} round {rnd}", (r, rnd)
+            dist.barrier()
+            for f in fds:
+                os.close(f)
+    elif case == "vmm":
+        # arenas allocated with virtual memory management and shared as descriptors: the layer must give the same bits
+        # as with CUDA IPC arenas (TERAMOE_ARENA=vmm is set by the test; use_fabric=True selects the same allocation)
+        T, H, I, E, K = 300, 512, 256, 8 * world, 4
+        prob = make_problem(world, T, H, I, E, K, seed=11, dtype=dtype, x_scale=0.5, w_scale=0.05, uneven_tokens=True)
+        ref = oracle(prob)[rank]
+        r = prob["ranks"][rank]
+        El = E // world
+        outs = []
+        for kind in ("ipc", "vmm", "fabric"):
+            buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True, use_fabric=(kind == "fabric"))
+            world_obj = buf._world
+            if kind == "vmm":
+                # the environment switch, set for this buffer only
+                buf.destroy()
+                from teramoe_b200.parallel import world as world_mod
+                world_mod.ARENA_KIND = "vmm"
+                buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True)
+                world_mod.ARENA_KIND = "ipc"
+                world_obj = buf._world
+            assert world_obj.control.is_vmm() == (kind != "ipc") and world_obj.data.is_vmm() == (kind != "ipc")
+            x = r["x"].to(dev).clone().requires_grad_(True)
+            w = r["w"].to(dev).clone().requires_grad_(True)
+            Wg = prob["W_gateup"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            Wd = prob["W_down"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            out = buf.teramoe_autograd(x, r["idx"].to(dev), w, Wg, Wd, E)
+            out.backward(r["go"].to(dev))
+            outs.append({"out": out.detach(), "dx": x.grad, "dw": w.grad, "dWg": Wg.grad, "dWd": Wd.grad})
+            # a larger call makes the data arena regrow: the new allocation is shared the same way
+            big = torch.randn(4096, 1024, dtype=dtype, device=dev)
+            bidx = torch.randint(0, E, (4096, K), device=dev)
+            rx, *_ = buf.deepep_dispatch(big, topk_idx=bidx, topk_weights=torch.ones(4096, K, device=dev), num_experts=E)
+            assert world_obj.data.is_vmm() == (kind != "ipc")
+            buf.check_status()
+            buf.destroy()
+        compare([outs[0]], [ref], tol, tol)
+        for other in outs[1:]:
+            for n in outs[0]:
+                assert torch.equal(outs[0][n], other[n]), f"{n} differs between arena kinds"
     elif case == "mismatch":
         # ranks disagree on num_experts: the host-side check must raise on every rank, nothing hangs
         buf = tm.Buffer(group, device=dev)

@@ -9,8 +9,16 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+def _free_port():
+    """A port nobody listens on right now (asked from the kernel), so consecutive launches never meet a socket in TIME_WAIT."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _launch(backend, case, world, timeout=300, extra_env=None):
-    port = 29600 + (os.getpid() % 300)
+    port = _free_port()
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -42,6 +50,19 @@ def test_gloo_mismatched_arguments_raise():
 def test_gloo_absent_rank_is_detected():
     """Host-side failure detection: a rank that leaves makes the others raise instead of hanging."""
     _launch("gloo", "absent", 2, timeout=120)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_descriptor_exchange_between_processes(world):
+    """SCM_RIGHTS plumbing of the virtual-memory arenas, with anonymous memory files standing in for allocations."""
+    _launch("gloo", "fdpass", world, timeout=120)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_nccl_layer_on_vmm_arenas():
+    """cuMemCreate arenas mapped through shared descriptors give the same bits as cudaMalloc + CUDA IPC arenas."""
+    _launch("nccl", "vmm", _world(), timeout=300)
 
 
 @pytest.mark.gpu
