@@ -21,7 +21,7 @@ def test_vmm_arena_allocates_views_and_closes():
     v = a.view(256, [1000], torch.int32)
     assert int(v.abs().sum()) == 0                                   # zero-filled like the cudaMalloc arena
     v.copy_(torch.arange(1000, dtype=torch.int32, device="cuda"))
-    assert int(a.view(256 + 4 * 999, [1], torch.int32)[0]) == 999
+    assert int(a.view(256 + 4 * 996, [4], torch.int32)[3]) == 999     # views start on 16-byte boundaries
     fd = a.export_fd()
     assert fd >= 0 and a.export_fd() == fd                           # one descriptor, owned by the arena
     with pytest.raises(RuntimeError):
