@@ -227,14 +227,18 @@ void fused_dispatch_gemm(int64_t kind, std::vector<torch::Tensor> gemm_t, std::v
 //   push_t : [slot_tk, slot_row, recv_row_base]
 //   red_t  : [landing view, out] (+ [gtw view, gtw_out] in backward)
 //   work_t : [work (int32, 4 per item), num_work, expert_units (int32, 2 per expert), sync (zeroed, 8 + max_units)]
+//   wire_t : [] = one row per (token, k) entry on the wire; [slot_src view (arena), blk_ready (zeroed, one int per 128-row
+//            block)] = one row per (token, rank), copied into the token's other slots on the receiver; offs then has a ninth
+//            entry, the byte offset of slot_src in the arenas
 void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::Tensor> layout, std::vector<torch::Tensor> send_t,
                std::vector<torch::Tensor> sym_t, std::vector<int64_t> offs, std::vector<torch::Tensor> push_t,
                std::vector<torch::Tensor> red_t, std::vector<torch::Tensor> work_t, int64_t E, int64_t N, int64_t rank, int64_t epoch,
                int64_t num_dispatch_clusters, int64_t group_units, int64_t lag_percent, int64_t min_lag_items, int64_t reduce_chunk,
                c10::optional<torch::Tensor> status, int64_t num_sms, c10::optional<torch::Tensor> stats,
-               c10::optional<torch::Tensor> x_rows, c10::optional<torch::Tensor> ok) {
+               c10::optional<torch::Tensor> x_rows, c10::optional<torch::Tensor> ok, std::vector<torch::Tensor> wire_t) {
     TORCH_CHECK(gemm_t.size() == (bwd ? 11u : 6u) && layout.size() == 7 && send_t.size() == (bwd ? 6u : 7u) && sym_t.size() == 5 &&
-                offs.size() == 8 && push_t.size() == 3 && red_t.size() == (bwd ? 4u : 2u) && work_t.size() == 4,
+                (offs.size() == 8 || offs.size() == 9) && push_t.size() == 3 && red_t.size() == (bwd ? 4u : 2u) && work_t.size() == 4 &&
+                (wire_t.empty() || (wire_t.size() == 2 && offs.size() == 9)),
                 "moe_layer: wrong argument lists");
     const torch::Tensor& slot_x = gemm_t[0];
     const int S = (int)slot_x.size(0), H = (int)slot_x.size(1);
@@ -328,6 +332,13 @@ void moe_layer(bool bwd, std::vector<torch::Tensor> gemm_t, std::vector<torch::T
     f.off_blk_cnt = offs[5];
     TORCH_CHECK(send_t[0].size(1) == H && send_t[0].size(0) == tk.T && S % 128 == 0 && sym_t[2].numel() >= S / 128, "moe_layer: shape mismatch");
     TORCH_CHECK(bwd ? (gemm_t[6].size(1) == 2 * p.I) : true, "moe_layer: preact shape");
+    if (!wire_t.empty()) {
+        f.wire_rank = 1;
+        f.slot_src = i32(wire_t[0], "slot_src");
+        f.blk_ready = i32(wire_t[1], "blk_ready");
+        f.off_slot_src = (uint64_t)offs[8];
+        TORCH_CHECK(wire_t[0].numel() >= S && wire_t[1].numel() >= S / 128 && offs[8] >= 0 && offs[8] % 16 == 0, "moe_layer: wire tables");
+    }
     p.status = opt_status(status);
     p.num_sms = (int)num_sms;
     if (ok.has_value()) p.geom_ok = i32(*ok, "ok");
@@ -585,7 +596,11 @@ void register_more(pybind11::module_& m) {
           py::arg("unit_blk"), py::arg("num_units"), py::arg("blk_group"), py::arg("unit_order"), py::arg("ok") = py::none());
     m.def("zero_pad_rows", &zero_pad_rows, py::arg("seg_offsets"), py::arg("expert_total_local"), py::arg("slot_x"), py::arg("ok") = py::none());
     m.def("fused_dispatch_gemm", &fused_dispatch_gemm);
-    m.def("moe_layer", &moe_layer);
+    m.def("moe_layer", &moe_layer, py::arg("bwd"), py::arg("gemm_t"), py::arg("layout"), py::arg("send_t"), py::arg("sym_t"), py::arg("offs"),
+          py::arg("push_t"), py::arg("red_t"), py::arg("work_t"), py::arg("E"), py::arg("N"), py::arg("rank"), py::arg("epoch"),
+          py::arg("num_dispatch_clusters"), py::arg("group_units"), py::arg("lag_percent"), py::arg("min_lag_items"), py::arg("reduce_chunk"),
+          py::arg("status"), py::arg("num_sms"), py::arg("stats"), py::arg("x_rows"), py::arg("ok"),
+          py::arg("wire_t") = std::vector<torch::Tensor>());
     m.def("moe_layer_max_work", &moe_layer_max_work);
     m.def("moe_layer_schedule", &moe_layer_schedule);
     m.def("ep_barrier", &ep_barrier, py::arg("signal_ptrs"), py::arg("rank"), py::arg("N"), py::arg("epoch"), py::arg("status"),

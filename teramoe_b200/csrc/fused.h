@@ -33,6 +33,15 @@ struct FusedArgs {
     const int* unit_order;         // units sorted by arrival group
     const int* seg_offsets;        // [El + 1]
     const int* expert_total_local; // [El]
+    // Whole-layer kernel only: one row per (token, destination rank) on the wire.  The entries of a token on one rank
+    // share the row that travels to the entry with the smallest slot there (its "home"); the others only get their
+    // table entries and `slot_src` = the home slot, and the receiver copies the row locally (gather warps) before it
+    // counts the block as ready.  0: one row per (token, k) entry, every slot is filled by its sender.
+    int wire_rank;
+    uint64_t off_slot_src;         // data arena: int per slot; -1 = the row itself arrives, else the slot to copy it from
+    const int* slot_src;           // this rank's view of that table
+    int* blk_ready;                // local, zero before the kernel: rows in place (arrived or copied) per 128-row block
+    int* replicate_counter;        // local, zero before the kernel: next unit (in arrival order) whose blocks get their copies
 };
 
 struct GemmArgsPublic {

@@ -7,6 +7,11 @@
 //   dispatch   the first `num_dispatch_clusters` pairs first stream this rank's routed rows straight into their
 //              final slot of the destination ranks' operand table (bulk copies through shared memory) and bump
 //              the destination's per-128-row arrival counters; then they become workers like the others.
+//              With `wire_rank` a token's row crosses the link once per destination rank: it goes to the entry
+//              with the smallest slot there, the token's other entries on that rank only get their table entries,
+//              and the receiver's gather warps copy the row into those slots (`replicate`) before the block counts
+//              as ready (reference: one message per (token, rank) and a local replicate,
+//              csrc/kernels/layout.cu:79-95, csrc/teramoe/teramoe_orchestrator.cu:1216-1269).
 //   scheduler  `layer_schedule_kernel`: orders the items.  Units (one or two 128-row blocks of one expert) are
 //              taken in arrival order and cut into batches of `group_units`; a batch's second GEMM follows its
 //              first GEMM at a distance of `lag_percent` of the next batch, so the intermediate activation is
@@ -64,6 +69,7 @@ struct LayerPhase {
 struct LayerArgs {
     LayerPhase ph[4];
     FusedArgs f;
+    __nv_bfloat16* slot_x;       // this rank's operand table (the replicate role copies rows inside it)
     const int4* work;
     const int* num_work;
     int max_work;
@@ -274,7 +280,7 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
             bool pend = false, pend_last = false;
             uint64_t pend_dst = 0;
             uint32_t pend_bytes = 0, pend_b = 0;
-            int pend_blk = 0, pend_d = 0;
+            int pend_blk = 0, pend_d = 0, pend_entry = 0;
             int pub_blk[kPublishBatchL], pub_d[kPublishBatchL], npub = 0;
             auto publish = [&]() {
                 if (npub == 0) return;
@@ -286,6 +292,20 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     if (i < npub) red_add_relaxed_sys_l(reinterpret_cast<int*>(f.ctrl_ptrs[pub_d[i]] + f.off_blk_cnt) + pub_blk[i], 1);
                 npub = 0;
             };
+            auto add_publish = [&](int blk, int d) {
+#pragma unroll
+                for (int i = 0; i < kPublishBatchL; ++i)
+                    if (i == npub) { pub_blk[i] = blk; pub_d[i] = d; }
+                if (++npub == kPublishBatchL) publish();
+            };
+            // wire_rank: slot of entry (t, k2) if it is another entry of token t on rank d (a sibling of the home entry), else -1
+            auto sibling_slot = [&](int t, int k, int k2, int d) -> int {
+                if (k2 == k) return -1;
+                const long long e2 = load_idx_l(f.topk_idx, f.idx_is64, (long)t * f.K + k2);
+                if (e2 < 0 || e2 >= f.E || (int)e2 / e_local != d) return -1;
+                const int s2 = f.send_slot[(long)t * f.K + k2];
+                return (s2 >= 0 && s2 < f.slot_cap) ? s2 : -1;
+            };
             auto store_pending = [&]() -> bool {
                 if (!pend) return true;
                 const uint32_t b = pend_b;
@@ -295,10 +315,16 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                 tma_store_commit();
                 pend = false;
                 if (pend_last) {
-#pragma unroll
-                    for (int i = 0; i < kPublishBatchL; ++i)
-                        if (i == npub) { pub_blk[i] = pend_blk; pub_d[i] = pend_d; }
-                    if (++npub == kPublishBatchL) publish();
+                    add_publish(pend_blk, pend_d);
+                    if (f.wire_rank) {
+                        // the row also stands for the token's other entries on that rank: their blocks count it too, and the
+                        // counts go out behind the same completed copy and fence as the home's
+                        const int t = pend_entry / f.K, k = pend_entry - t * f.K;
+                        for (int k2 = 0; k2 < f.K; ++k2) {
+                            const int s2 = sibling_slot(t, k, k2, pend_d);
+                            if (s2 >= 0) add_publish(s2 >> 7, pend_d);
+                        }
+                    }
                 }
                 return true;
             };
@@ -309,6 +335,16 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                 const int slot = f.send_slot[entry];
                 if (slot < 0 || slot >= f.slot_cap || e < 0 || e >= f.E) continue;   // never store outside the destination table
                 const int d = e / e_local;
+                if (f.wire_rank) {
+                    // only the home entry of (t, d) travels: the one with the smallest slot, which is also the first of them
+                    // in sending order and the first the receiver works on
+                    bool home = true;
+                    for (int k2 = 0; k2 < f.K; ++k2) {
+                        const int s2 = sibling_slot(t, k, k2, d);
+                        if (s2 >= 0 && s2 < slot) home = false;
+                    }
+                    if (!home) continue;
+                }
                 const uint64_t arena = f.arena_ptrs[d];
                 const uint8_t* src = reinterpret_cast<const uint8_t*>(f.x) + (size_t)t * row_bytes;
                 const uint64_t dst = arena + f.off_slot_x + (uint64_t)slot * row_bytes;
@@ -327,13 +363,29 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     pend_last = off + kDispatchChunkL >= row_bytes;
                     pend_blk = slot >> 7;
                     pend_d = d;
+                    pend_entry = entry;
+                    if (off == 0 && f.wire_rank) {
+                        // where every slot of (t, d) gets its row from, and the table entries of the slots that get no row
+                        const int row = f.send_row[(long)t * f.N + d];
+                        reinterpret_cast<int*>(arena + f.off_slot_src)[slot] = -1;
+                        for (int k2 = 0; k2 < f.K; ++k2) {
+                            const int s2 = sibling_slot(t, k, k2, d);
+                            if (s2 < 0) continue;
+                            reinterpret_cast<int*>(arena + f.off_slot_src)[s2] = slot;
+                            if (f.with_meta) {
+                                reinterpret_cast<float*>(arena + f.off_slot_w)[s2] = f.topk_w[(long)t * f.K + k2];
+                                reinterpret_cast<int*>(arena + f.off_slot_tk)[s2] = t * f.K + k2;
+                                reinterpret_cast<int*>(arena + f.off_slot_row)[s2] = row;
+                            }
+                        }
+                    }
                     if (off == 0 && f.with_meta) {
                         const int row = f.send_row[(long)t * f.N + d];
                         reinterpret_cast<float*>(arena + f.off_slot_w)[slot] = f.topk_w[entry];
                         reinterpret_cast<int*>(arena + f.off_slot_tk)[slot] = entry;
                         reinterpret_cast<int*>(arena + f.off_slot_row)[slot] = row;
-                        bool first = true;                       // first entry of token t that goes to rank d
-                        for (int k2 = 0; k2 < k; ++k2) {
+                        bool first = true;                       // first entry of token t that goes to rank d (wire_rank: the home is the only one)
+                        for (int k2 = 0; k2 < k && !f.wire_rank; ++k2) {
                             const long long e2 = load_idx_l(f.topk_idx, f.idx_is64, (long)t * f.K + k2);
                             if (e2 >= 0 && e2 < f.E && (int)e2 / e_local == d) first = false;
                         }
@@ -353,6 +405,55 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
     // Sums each token's landed rows once every rank has said that its pushes are complete.  Warps 2 and 3 of every CTA
     // do nothing else (in backward their memory traffic runs under the weight-gradient GEMMs); the epilogue warps join
     // when the work list is exhausted.  Token chunks come from their own counter.
+    auto replicate_loop = [&]() {
+        // wire_rank: units in arrival order; when the rows of a block have been counted in (rows that arrived, and for the
+        // others the word that says which slot holds their row, sent behind that row), copy the missing rows and
+        // declare the block ready.  The first GEMM's producers wait for `blk_ready` instead of the arrival counters.
+        const int nvec = f.H / 8;
+        const GemmArgs& g0 = L.ph[0].g;
+        const int* slot_src = f.slot_src;
+        while (true) {
+            int i = 0;
+            if (lane == 0) i = atomicAdd(f.replicate_counter, 1);
+            i = __shfl_sync(0xffffffffu, i, 0);
+            if (i >= num_units) break;
+            const int u = f.unit_order[i];
+            const int b0 = g0.unit_blk[u], b1 = g0.unit_blk[u + 1];
+            for (int b = b0; b < b1; ++b) {
+                const int le = g0.mblock_expert[b];
+                const int valid_end = f.seg_offsets[le] + f.expert_total_local[le];
+                const int need = max(0, min(128, valid_end - b * 128));
+                if (need == 0) continue;
+                int got = 1;
+                if (lane == 0) got = wait_flag_ge_sys(f.blk_cnt + b, need, L.status, 604) ? 1 : 0;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                __syncwarp();                                       // the other lanes read behind lane 0's acquire
+                if (!got) return;                                   // reported; the producers' wait on blk_ready runs out the same way
+                for (int r = 0; r < need; ++r) {
+                    const int sl = b * 128 + r;
+                    const int src = __ldcg(slot_src + sl);
+                    if (src < 0 || src >= f.slot_cap || src == sl) continue;
+                    const int4* srow = reinterpret_cast<const int4*>(L.slot_x + (long)src * f.H);
+                    int4* drow = reinterpret_cast<int4*>(L.slot_x + (long)sl * f.H);
+                    for (int v = lane; v < nvec; v += 128) {          // four 16-byte loads in flight per lane
+                        int4 t0 = ld_cg_v4(srow + v), t1 = make_int4(0, 0, 0, 0), t2 = t1, t3 = t1;
+                        if (v + 32 < nvec) t1 = ld_cg_v4(srow + v + 32);
+                        if (v + 64 < nvec) t2 = ld_cg_v4(srow + v + 64);
+                        if (v + 96 < nvec) t3 = ld_cg_v4(srow + v + 96);
+                        drow[v] = t0;
+                        if (v + 32 < nvec) drow[v + 32] = t1;
+                        if (v + 64 < nvec) drow[v + 64] = t2;
+                        if (v + 96 < nvec) drow[v + 96] = t3;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    fence_acq_rel_gpu();
+                    red_add_release_gpu(f.blk_ready + b, need);
+                }
+            }
+        }
+    };
     auto expand_loop = [&]() {
         // X back into slot space, eight rows per claim, four 16-byte loads in flight per lane
         const int nvec = f.H / 8;
@@ -512,7 +613,7 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
                     if (q.kind == kWorkGemm1) {
                         // rows of this block come from the ranks' dispatch pairs
                         if (!q.live || q.need == 0) return 1;
-                        const int* flag = f.blk_cnt + q.m0 / BM;
+                        const int* flag = (f.wire_rank ? f.blk_ready : f.blk_cnt) + q.m0 / BM;
                         if (ld_acquire_sys(flag) >= q.need) return 1;
                         if (!block) return 0;
                         const uint64_t t0 = globaltimer_ns();
@@ -748,6 +849,7 @@ moe_layer_kernel(const __grid_constant__ LayerArgs L) {
             tma_store_wait<0>();
             if (ok) gather_loop();            // the list is done: help with the landed rows
         } else if (warp >= 2) {
+            if (f.wire_rank) replicate_loop();
             if constexpr (BWD) {
                 if (L.xperm != nullptr) expand_loop();
             }
@@ -996,6 +1098,11 @@ cudaError_t moe_layer_launch(const LayerParams& p, cudaStream_t stream) {
     }
     L.f = p.f;
     L.f.tile_counter = nullptr;
+    L.slot_x = static_cast<__nv_bfloat16*>(const_cast<void*>(p.slot_x));
+    if (p.f.wire_rank) {
+        if (p.f.slot_src == nullptr || p.f.blk_ready == nullptr || p.f.off_slot_src % 4 != 0) return cudaErrorInvalidValue;
+        L.f.replicate_counter = p.sync + 6;
+    }
     L.work = static_cast<const int4*>(p.work);
     L.num_work = p.num_work;
     L.max_work = p.max_work;

@@ -62,7 +62,7 @@ struct LayerParams {
     int max_work;
     int* num_work;                 // device scalar written by the scheduler kernel
     int* expert_units;             // int2 [El]: first unit and unit count of every local expert (written by the scheduler)
-    int* sync;                     // [8 + max_units]: item counter, finished-push counter, complete units, gather token counter, X rows claimed / filled, 2 spare,
+    int* sync;                     // [8 + max_units]: item counter, finished-push counter, complete units, gather token counter, X rows claimed / filled, next unit of the replicate role, 1 spare,
                                    //   finished first-GEMM warps per unit
     int group_units;               // units per batch of the schedule (compute_batch_size / 256)
     int lag_percent;               // how far (percent of a batch) the first GEMM runs ahead before the batch's second GEMM starts

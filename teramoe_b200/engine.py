@@ -85,7 +85,8 @@ OVERLAP_BWD_COMBINE = os.environ.get("TERAMOE_OVERLAP_BWD_COMBINE", "0") == "1"
 OVERLAP_COMM_SMS = int(os.environ.get("TERAMOE_OVERLAP_COMM_SMS", "8"))
 
 TABLES = ("recv_x", "slot_row", "slot_w", "slot_tk", "row_tok", "row_land", "row_slots", "landing", "gtw", "row_topk_idx", "row_topk_w")
-EXTRA_TABLES = ("slot_x", "row_first")       # fused dispatch: slot-space operand rows, first slot of every received row
+EXTRA_TABLES = ("slot_x", "row_first", "slot_src")   # fused dispatch: slot-space operand rows, first slot of every received row,
+                                                     # slot that holds a slot's row (once-per-rank wire format)
 
 # Dispatch fused into the GEMM that consumes it (csrc/fused.cu): one cooperative kernel, a few CTA pairs
 # push rows to the peers while the others run the gate_up (forward) / grad_act (backward) GEMM on the
@@ -117,6 +118,14 @@ _LAYER_KERNEL_MODE = os.environ.get("TERAMOE_LAYER_KERNEL", "auto")
 NVTX_MARKS = os.environ.get("TERAMOE_NVTX", "0") == "1"
 # Enqueue the whole forward before the host has read the layout sizes (see EPEngine.layout_gen); "0" waits for them first.
 LAUNCH_AHEAD = os.environ.get("TERAMOE_LAUNCH_AHEAD", "1") == "1"
+# Wire format of the dispatch inside the layer kernel.  "entry": one row per (token, k) entry, written by its sender straight
+# into the entry's slot.  "rank": one row per (token, destination rank): it goes to the token's first slot on that rank and
+# the receiver's gather warps copy it into the token's other slots there (top-8 over 8 ranks: 539 instead of 822 MB per rank
+# and transfer on the headline shape).  Results are bit-identical.  Default "entry": the transfer is hidden behind the
+# GEMMs at EP <= 8 on this shape (producers wait 0.35 ms per pair for arrivals at EP=8), and "rank" adds a local copy pass.
+LAYER_WIRE = os.environ.get("TERAMOE_WIRE", "entry")
+if LAYER_WIRE not in ("entry", "rank"):
+    raise ValueError(f"TERAMOE_WIRE must be 'entry' or 'rank', not {LAYER_WIRE!r}")
 LAYER_REDUCE_CHUNK = 64          # tokens per reduce item
 LAYER_MIN_LAG_PER_PAIR = float(os.environ.get("TERAMOE_LAYER_MIN_LAG", "2"))
 
@@ -193,7 +202,7 @@ def _table_sizes(maxima, H: int, K: int):
         "recv_x": rmax * H * 2, "slot_row": smax * 4, "slot_w": smax * 4, "slot_tk": smax * 4,
         "row_tok": rmax * 4, "row_land": rmax * 4, "row_slots": rmax * K * 4,
         "landing": lmax * H * 2, "gtw": tmax * K * 4, "row_topk_idx": rmax * K * 8, "row_topk_w": rmax * K * 4,
-        "slot_x": smax * H * 2, "row_first": rmax * 4,
+        "slot_x": smax * H * 2, "row_first": rmax * 4, "slot_src": smax * 4,
     }
     return sizes, (rmax, smax, lmax, tmax)
 
@@ -279,7 +288,8 @@ class EPEngine:
                 "row_topk_idx": v(offs["row_topk_idx"], [rmax, K], torch.int64),
                 "row_topk_w": v(offs["row_topk_w"], [rmax, K], torch.float32),
                 **({"slot_x": v(offs["slot_x"], [smax, H], torch.bfloat16),
-                    "row_first": v(offs["row_first"], [rmax], torch.int32)} if "slot_x" in offs else {}),
+                    "row_first": v(offs["row_first"], [rmax], torch.int32),
+                    "slot_src": v(offs["slot_src"], [smax], torch.int32)} if "slot_x" in offs else {}),
             }
         t = w.cpu_tables
         shapes = {"recv_x": ((rmax, H), dtype), "slot_row": ((smax,), torch.int32), "slot_w": ((smax,), torch.float32),
@@ -833,6 +843,10 @@ class EPEngine:
         # per-role wait times of this launch (ns summed over waiting threads), kept on the device until somebody asks
         wait_ns = torch.zeros(24, dtype=torch.int64, device=dev)
         self.last_wait_ns[kind] = wait_ns
+        wire_t = []
+        if (opts.get("wire") or LAYER_WIRE) == "rank":
+            wire_t = [tabs["slot_src"], torch.zeros(tabs["slot_x"].shape[0] // 128, **i32)]
+            offsets.append(offs["slot_src"])
         epoch = w.next_epoch()
         if ahead and T > h.maxima[3]:
             # more tokens here than the tables were sized for: the device flag is 0 on EVERY rank (the maximum over ranks
@@ -841,7 +855,7 @@ class EPEngine:
         else:
             ext.moe_layer(bwd, gemm_t, layout, send_t, sym_t, offsets, push_t, red_t, work_t, E, N, h.rank, epoch,
                           dispatch_pairs(kind, h.num_dispatch_sms), group_units, lag, min_lag, LAYER_REDUCE_CHUNK, w.status, num_sms, wait_ns,
-                          saved.saved_x if (bwd and S > 0) else None, ok)
+                          saved.saved_x if (bwd and S > 0) else None, ok, wire_t)
         # every row meant for this rank has arrived once the kernel is done: clear the arrival counters for the next use
         w.blk_cnt_view()[: max(S // 128, 1)].zero_()
         if bwd:

@@ -83,6 +83,32 @@ def main():
             err = (fp8_dequantize(rq, rsc, torch.float32) - want.float()).abs().max().item()
             assert err <= 0.07 * max(1.0, want.float().abs().max().item()), err
         buf.destroy()
+    elif case == "wire_rank":
+        # one row per (token, rank) on the wire (TERAMOE_WIRE=rank, set by the test) against one row per entry: same bits
+        from teramoe_b200 import engine
+        T, H, I, E, K = 384, 1024, 1536, 4 * world, 6
+        prob = make_problem(world, T, H, I, E, K, seed=23, dtype=dtype, x_scale=0.5, w_scale=0.05, drop_some=True, uneven_tokens=True)
+        ref = oracle(prob)[rank]
+        r = prob["ranks"][rank]
+        El = E // world
+        buf = tm.Buffer(group, int(1e6) // 128 * 128, explicitly_destroy=True)
+        res = {}
+        for wire in ("entry", "rank", "rank"):
+            engine.LAYER_WIRE = wire
+            x = r["x"].to(dev).clone().requires_grad_(True)
+            w = r["w"].to(dev).clone().requires_grad_(True)
+            Wg = prob["W_gateup"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            Wd = prob["W_down"][rank * El:(rank + 1) * El].to(dev).clone().requires_grad_(True)
+            out = buf.teramoe_autograd(x, r["idx"].to(dev), w, Wg, Wd, E)
+            out.backward(r["go"].to(dev))
+            assert buf._engine.last_paths.get("layer_kernel", False), "the default rules must pick the layer kernel for this shape"
+            res.setdefault(wire, []).append({"out": out.detach(), "dx": x.grad, "dw": w.grad, "dWg": Wg.grad, "dWd": Wd.grad})
+        compare([res["rank"][0]], [ref], tol, tol)
+        for n in res["entry"][0]:
+            assert torch.equal(res["entry"][0][n], res["rank"][0][n]), f"{n}: wire formats differ"
+            assert torch.equal(res["rank"][0][n], res["rank"][1][n]), f"{n}: two runs differ"
+        buf.check_status()
+        buf.destroy()
     elif case == "layer_auto":
         # a shape large enough for the default rules to pick the fused kernels (I >= 1536): no environment switches
         from teramoe_b200 import engine

@@ -142,6 +142,33 @@ def test_layer_kernel_ep1_matches_oracle_and_separate_kernels(T, H, I, E, K, kw,
     buf.destroy()
 
 
+@pytest.mark.parametrize("T,H,I,E,K,kw", [
+    (700, 512, 1536, 8, 4, {}),
+    (1500, 1024, 512, 16, 8, {"stage": 2, "num_dispatch_sms": 8}),
+    (77, 256, 128, 8, 3, {"total_sms": 64, "num_dispatch_sms": 4}),
+])
+def test_layer_kernel_one_row_per_rank_on_the_wire_is_bitwise_equal(T, H, I, E, K, kw, monkeypatch):
+    """TERAMOE_WIRE=rank: a token's row travels once per destination rank and the receiver copies it into the token's other
+    slots there.  On one rank all K entries of a token share one row, so every block mixes arrived and copied rows."""
+    from teramoe_b200 import engine
+    _set_path(monkeypatch, "layer")
+    prob = make_problem(1, T, H, I, E, K, seed=T + 1, dtype=torch.bfloat16, device="cuda", x_scale=0.1, w_scale=0.02, drop_some=True,
+                        empty_expert=1)
+    buf = tm.Buffer(None, int(64e6), explicitly_destroy=True)
+    res = {}
+    for wire in ("entry", "rank", "entry", "rank"):
+        monkeypatch.setattr(engine, "LAYER_WIRE", wire)
+        res.setdefault(wire, []).append(_run(buf, prob, E, **kw))
+        assert buf._engine.last_paths.get("layer_kernel", False)
+    ref = oracle(prob)[0]
+    for name in ("out", "dx", "dw", "dWg", "dWd"):
+        assert_close_bf16(res["rank"][0][name].float(), ref[name].cuda().float(), name)
+        assert torch.equal(res["rank"][0][name], res["entry"][0][name]), f"{name}: wire formats differ"
+        assert torch.equal(res["rank"][1][name], res["entry"][1][name]), f"{name}: wire formats differ on the second call"
+    buf.check_status()
+    buf.destroy()
+
+
 def test_layer_kernel_zero_tokens_and_changing_routing(monkeypatch):
     """A call without tokens, then calls whose routing changes every step, on one buffer."""
     _set_path(monkeypatch, "layer")

@@ -99,6 +99,12 @@ def _world():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
+def test_nccl_layer_kernel_one_row_per_rank_on_the_wire():
+    _launch("nccl", "wire_rank", _world(), timeout=300)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
 def test_nccl_soak_changing_routing_interleaved_layers():
     """Race / reuse soak (the reference's accuracy script repeats 10,000 identical steps,
     tests/test_teramoe_accuracy.py:296-305; here every step is different): see the "soak" case of mp_worker.py."""
