@@ -292,8 +292,8 @@ class Buffer(LowLatencyMixin):
         LOCAL expert ids (-1 for experts of other ranks, weights zeroed there), like
         csrc/kernels/intranode.cu:369-378.  With `handle=` (cached mode) only the payload moves and
         no host synchronisation happens.  `num_worst_tokens > 0` gives fixed-shape outputs (padded rows are
-        zero, expert id -1, empty per-expert list); the 32-byte read of the layout sizes still happens, since
-        the arena geometry is sized per call."""
+        zero, expert id -1, empty per-expert list) without any host wait: the tables are sized for that many rows
+        and the layout sizes stay on the device (`_dispatch_fixed_shape`)."""
         if isinstance(x, tuple):
             # FP8 payload (x_e4m3 [T,H], scales [T,H/128] fp32), teramoe/buffer.py:344-346: both parts travel as raw
             # bytes through the same kernels (the second with the cached handle) and come back as a tuple
