@@ -121,6 +121,32 @@ def send_layout(topk_idx: torch.Tensor, E: int, N: int, rank: int, gl: GlobalLay
     return SendLayout(send_slot.to(torch.int32), send_row.to(torch.int32), land_off.to(torch.int32), ndst.to(torch.int32))
 
 
+def wire_rank_plan(topk_idx: torch.Tensor, send_slot: torch.Tensor, E: int, N: int):
+    """Once-per-rank wire format of the layer kernel's dispatch (csrc/layer.cu, `wire_rank`), as index math.
+
+    Of a token's entries on one destination rank only the HOME entry carries the row: the one with the smallest slot
+    there (slots of a rank grow with the local expert id, so the home is also the first of them the receiver works on).
+    The other entries (siblings) get their table entries and `slot_src` = the home's slot; the receiver copies the row.
+
+    -> (home [T,K] bool, src_slot [T,K] int64): src_slot is -1 for invalid entries and for homes, else the home's slot on
+    the same rank.  Rows on the wire = home.sum(): one per (token, destination rank)."""
+    idx = topk_idx.detach().cpu().long()
+    slot = send_slot.detach().cpu().long().view(idx.shape)
+    T, K = idx.shape
+    El = E // N
+    valid = (idx >= 0) & (idx < E) & (slot >= 0)
+    dst = torch.where(valid, idx // El, torch.full_like(idx, -1))
+    big = torch.iinfo(torch.int64).max
+    home_slot = torch.full((T, K), -1, dtype=torch.int64)
+    for d in range(N):
+        on_d = dst == d
+        smallest = torch.where(on_d, slot, torch.full_like(slot, big)).min(dim=1, keepdim=True).values     # [T,1]
+        home_slot = torch.where(on_d, smallest.expand(T, K), home_slot)
+    home = valid & (slot == home_slot)
+    src_slot = torch.where(valid & ~home, home_slot, torch.full_like(slot, -1))
+    return home, src_slot
+
+
 def recv_tables(rank: int, E: int, N: int, gl: GlobalLayout):
     """This rank's segment table and block->expert map: (seg_offsets [El+1], mblock_expert [S/128])."""
     El = E // N

@@ -78,3 +78,35 @@ def test_fusion_rule_follows_flops_per_wire_byte():
     if eng.USE_CTA_PAIRS and not eng.USE_TMA_GATHER:
         assert eng.use_fused_dispatch(2048, 8, 0) and not eng.use_fused_dispatch(512, 8, 0)
         assert not eng.use_fused_dispatch(2048, 8, eng.FUSED_DISPATCH_MAX_BYTES + 1)
+
+
+@pytest.mark.parametrize("N,T,E,K", [(1, 200, 8, 4), (4, 333, 32, 8), (8, 257, 64, 6)])
+def test_once_per_rank_wire_plan_covers_every_slot_once(N, T, E, K):
+    """Index math of the layer kernel's once-per-rank wire format: one home per (token, destination rank), every other
+    entry of the token on that rank points at the home's slot, and the rows on the wire are the distinct-rank count."""
+    from teramoe_b200 import layout as L
+    g = torch.Generator().manual_seed(N * 1000 + T)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)])
+    idx[torch.rand(T, K, generator=g) < 0.1] = -1
+    metas = torch.stack([L.count_row(idx, E, N) for _ in range(N)])          # every rank routes the same tokens here
+    gl = L.global_layout(metas, E, N)
+    sl = L.send_layout(idx, E, N, 0, gl)
+    home, src = L.wire_rank_plan(idx, sl.send_slot, E, N)
+    valid = idx >= 0
+    hits = L.token_rank_hits(idx, E, N)
+    assert int(home.sum()) == int(hits.sum())                                # one row per (token, rank) on the wire
+    assert bool((home <= valid).all()) and bool((src[~valid] == -1).all()) and bool((src[home] == -1).all())
+    El = E // N
+    slot = sl.send_slot.long()
+    for t in range(T):
+        for d in range(N):
+            ks = [k for k in range(K) if valid[t, k] and int(idx[t, k]) // El == d]
+            if not ks:
+                continue
+            homes = [k for k in ks if home[t, k]]
+            assert len(homes) == 1
+            h = homes[0]
+            assert int(slot[t, h]) == min(int(slot[t, k]) for k in ks)       # the first slot the receiver works on
+            for k in ks:
+                if k != h:
+                    assert int(src[t, k]) == int(slot[t, h]) and int(src[t, k]) < int(slot[t, k])
