@@ -110,3 +110,18 @@ def test_once_per_rank_wire_plan_covers_every_slot_once(N, T, E, K):
             for k in ks:
                 if k != h:
                     assert int(src[t, k]) == int(slot[t, h]) and int(src[t, k]) < int(slot[t, k])
+
+
+def test_bench_reference_arm_prints_its_unavailable_line_and_exits_zero():
+    """Contract of the benchmark's reference arm where the reference cannot be installed: one JSON line, exit code 0."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    rec = json.loads(lines[0])
+    assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and "\n" not in rec["unavailable"]
