@@ -74,6 +74,10 @@ def exchange_fds(fd: int, rank: int, size: int, group=None, gather=None) -> List
             a, _addr = listener.accept()
             try:
                 a.settimeout(_TIMEOUT_S)
+                # the socket name is unguessable, but an allocation is only ever handed to a process of the same user
+                _pid, uid, _gid = struct.unpack("3i", a.getsockopt(socket.SOL_SOCKET, socket.SO_PEERCRED, struct.calcsize("3i")))
+                if uid != os.getuid():
+                    raise RuntimeError(f"teramoe_b200: descriptor requested by a process of another user (uid {uid})")
                 (peer,) = struct.unpack("<i", _recv_exact(a, 4))
                 if not (0 <= peer < size) or peer == rank:
                     raise RuntimeError(f"teramoe_b200: descriptor requested by an unknown rank {peer}")
