@@ -125,3 +125,67 @@ def test_bench_reference_arm_prints_its_unavailable_line_and_exits_zero():
     assert len(lines) == 1
     rec = json.loads(lines[0])
     assert rec["impl"] == "reference" and isinstance(rec["unavailable"], str) and "\n" not in rec["unavailable"]
+
+
+def _layout_invariants(idx_per_rank, E, N):
+    """Every routed entry gets its own slot inside its expert's segment, every (token, rank) hit its own receive row, landing
+    rows tile [0, land_rows) -- for ALL ranks together, which is what makes the push model race-free."""
+    from teramoe_b200 import layout as L
+    El = E // N
+    metas = torch.stack([L.count_row(idx, E, N) for idx in idx_per_rank])
+    gl = L.global_layout(metas, E, N)
+    slots_seen = [set() for _ in range(N)]
+    rows_seen = [set() for _ in range(N)]
+    for r, idx in enumerate(idx_per_rank):
+        sl = L.send_layout(idx, E, N, r, gl)
+        idx = idx.long()
+        valid = (idx >= 0) & (idx < E)
+        assert bool((sl.send_slot[~valid] == -1).all())
+        for t, k in valid.nonzero().tolist():
+            e = int(idx[t, k])
+            d, s = e // El, int(sl.send_slot[t, k])
+            lo = int(gl.seg_off_all[e])
+            assert lo <= s < lo + int(gl.expert_total[e]), "slot outside the expert's rows"
+            assert s not in slots_seen[d], "two entries share a slot"
+            slots_seen[d].add(s)
+        hit = L.token_rank_hits(idx, E, N)
+        assert torch.equal(hit, sl.send_row >= 0)
+        for t, d in hit.nonzero().tolist():
+            row = int(sl.send_row[t, d])
+            assert 0 <= row < int(gl.rows[d]) and row not in rows_seen[d]
+            rows_seen[d].add(row)
+        assert torch.equal(sl.ndst.long(), hit.sum(1))
+        if idx.shape[0]:
+            assert int(sl.land_off[0]) == 0 and torch.equal(sl.land_off[1:].long(), torch.cumsum(sl.ndst.long(), 0)[:-1])
+            assert int(sl.land_off[-1]) + int(sl.ndst[-1]) == int(gl.land_rows[r])
+    for d in range(N):
+        assert len(slots_seen[d]) == int(gl.expert_total.view(N, El)[d].sum()) and len(rows_seen[d]) == int(gl.rows[d])
+        assert int(gl.slots_padded[d]) % 128 == 0 and int(gl.slots_padded[d]) >= len(slots_seen[d])
+
+
+def test_layout_invariants_on_edge_cases():
+    g = torch.Generator().manual_seed(5)
+    cases = [
+        (1, 4, [torch.zeros(0, 2, dtype=torch.int64)]),                                        # no tokens at all
+        (2, 4, [torch.full((7, 3), -1, dtype=torch.int64), torch.zeros(0, 3, dtype=torch.int64)]),   # nothing routed
+        (2, 2, [torch.tensor([[0, 1], [1, 0], [1, -1]]), torch.tensor([[1, 1]])]),             # E == N, a token twice on one expert
+        (4, 8, [torch.randint(-1, 8, (300, 1), generator=g) for _ in range(4)]),               # K == 1
+        (8, 64, [torch.randint(0, 64, (129 + 31 * r, 8), generator=g) for r in range(8)]),     # duplicates inside a token, uneven T
+    ]
+    for N, E, idx_per_rank in cases:
+        _layout_invariants(idx_per_rank, E, N)
+
+
+def test_layout_invariants_random():
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=25, deadline=None)
+    @given(st.sampled_from([1, 2, 4, 8]), st.integers(1, 4), st.integers(1, 6), st.integers(0, 70), st.integers(0, 2 ** 31 - 1))
+    def run(N, el, K, T, seed):
+        E = N * el
+        g = torch.Generator().manual_seed(seed)
+        idx_per_rank = [torch.randint(-1, E, (max(0, T - 9 * r), K), generator=g) for r in range(N)]
+        _layout_invariants(idx_per_rank, E, N)
+
+    run()
