@@ -4,6 +4,7 @@ Reference counterparts: teramoe/buffer.py:32-147 (construction / destroy), :153-
 :293-454 (layout, dispatch, combine), :537-708 (low-latency API), :710-818 (fused autograd entry
 points).  Differences that matter to callers:
 
+* `comm=` (an mpi4py communicator instead of a group) only carries the rendezvous of a process group, see `_group_from_mpi`.
 * One NVSwitch node only (EP = 1, 2, 4, 8): `num_rdma_bytes`, `num_qps_per_rank`, `allow_mnnvl` are accepted and
   ignored; the documented constructor call works on <= 8 ranks (the reference rejects it there,
   csrc/moe_extension.cpp:161-162).
@@ -74,6 +75,33 @@ class _TeraMoEFunction(torch.autograd.Function):
         return None, dx, None, gtw, dWgu, dWd, None, None, None
 
 
+def _group_from_mpi(comm, want_cuda: bool):
+    """A torch.distributed group over the ranks of an mpi4py-style communicator (`Get_rank`, `Get_size`, `bcast`,
+    `allgather`), for callers that launch with MPI and have no process group yet (reference: teramoe/buffer.py:78-86, which
+    all-gathers its handles through the communicator itself).  Here the communicator only carries the rendezvous: rank 0
+    picks a free port on the loop-back interface (all ranks sit on one node), everybody joins a process group there, and
+    the rest of the bootstrap is the usual one.  With a process group already initialised the communicator must span it."""
+    rank, size = int(comm.Get_rank()), int(comm.Get_size())
+    if size == 1:
+        return None
+    if size > 8:
+        raise ValueError("teramoe_b200 runs on one NVSwitch node: at most 8 ranks")
+    if dist.is_initialized():
+        members = sorted(int(r) for r in comm.allgather(dist.get_rank()))
+        if members != list(range(dist.get_world_size())):
+            raise ValueError("the communicator covers only part of the initialised process group: pass `group=` instead")
+        return dist.group.WORLD
+    endpoint = None
+    if rank == 0:
+        import socket
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            s.bind(("127.0.0.1", 0))
+            endpoint = ("127.0.0.1", s.getsockname()[1])
+    addr, port = comm.bcast(endpoint, root=0)
+    dist.init_process_group("nccl" if want_cuda else "gloo", init_method=f"tcp://{addr}:{port}", rank=rank, world_size=size)
+    return dist.group.WORLD
+
+
 class Buffer(LowLatencyMixin):
     """Expert-parallel communication + fused MoE layer on one NVSwitch node."""
 
@@ -86,7 +114,8 @@ class Buffer(LowLatencyMixin):
         if num_nvl_bytes % 128 != 0 or num_rdma_bytes % 128 != 0:
             raise ValueError("buffer sizes must be multiples of 128 bytes")
         if comm is not None and group is None:
-            raise NotImplementedError("mpi4py bootstrap is not available; pass a torch.distributed group")
+            want_cuda = torch.cuda.is_available() and (device is None or torch.device(device).type == "cuda")
+            group = _group_from_mpi(comm, want_cuda)
         if group is None and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             group = dist.group.WORLD
         if device is None:

@@ -17,9 +17,81 @@ import teramoe_b200 as tm
 from helpers import compare, make_problem, oracle
 
 
+class FileComm:
+    """Stand-in for an mpi4py communicator (Get_rank / Get_size / bcast / allgather) over a shared directory."""
+
+    def __init__(self, root, rank, size):
+        self.root, self.rank, self.size, self.seq = root, rank, size, 0
+
+    def Get_rank(self):
+        return self.rank
+
+    def Get_size(self):
+        return self.size
+
+    def _put(self, tag, obj):
+        import pickle
+        tmp = os.path.join(self.root, f".{tag}.{self.rank}.tmp")
+        with open(tmp, "wb") as f:
+            pickle.dump(obj, f)
+        os.replace(tmp, os.path.join(self.root, f"{tag}.{self.rank}"))
+
+    def _get(self, tag, r):
+        import pickle
+        import time
+        path = os.path.join(self.root, f"{tag}.{r}")
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > 60:
+                raise TimeoutError(path)
+            time.sleep(0.01)
+        with open(path, "rb") as f:
+            return pickle.load(f)
+
+    def allgather(self, obj):
+        self.seq += 1
+        self._put(f"ag{self.seq}", obj)
+        return [self._get(f"ag{self.seq}", r) for r in range(self.size)]
+
+    def bcast(self, obj, root=0):
+        self.seq += 1
+        if self.rank == root:
+            self._put(f"bc{self.seq}", obj)
+        return self._get(f"bc{self.seq}", root)
+
+
+def mpi_comm_case(backend):
+    """No process group yet: the buffer builds one from the communicator, then the layer runs as usual."""
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    assert backend == "gloo" and not dist.is_initialized()
+    comm = FileComm(os.environ["FILECOMM_DIR"], rank, world)
+    buf = tm.Buffer(comm=comm, device="cpu")
+    assert dist.is_initialized() and buf.group_size == world and buf.rank == rank
+    T, H, I, E, K = 40, 64, 96, 4 * world, 2
+    prob = make_problem(world, T, H, I, E, K, seed=9, dtype=torch.float32, x_scale=0.5, w_scale=0.05, uneven_tokens=True)
+    ref = oracle(prob)[rank]
+    r = prob["ranks"][rank]
+    El = E // world
+    x = r["x"].clone().requires_grad_(True)
+    w = r["w"].clone().requires_grad_(True)
+    Wg = prob["W_gateup"][rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    Wd = prob["W_down"][rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    out = buf.teramoe_autograd(x, r["idx"], w, Wg, Wd, E)
+    out.backward(r["go"])
+    compare([{"out": out.detach(), "dx": x.grad, "dw": w.grad, "dWg": Wg.grad, "dWd": Wd.grad}], [ref], 1e-4, 1e-4)
+    # a second buffer on the now initialised group: the communicator must span it
+    buf2 = tm.Buffer(comm=comm, device="cpu")
+    assert buf2.group_size == world
+    dist.barrier()
+    print(f"WORKER_OK {rank}", flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     backend, case = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if case == "mpi_comm":
+        return mpi_comm_case(backend)
     if backend == "nccl":
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dev = torch.device("cuda", torch.cuda.current_device())

@@ -43,6 +43,11 @@ def test_gloo_layer(world):
     _launch("gloo", "layer", world)
 
 
+def test_gloo_bootstrap_from_an_mpi_style_communicator(tmp_path):
+    """`Buffer(comm=...)`: no process group exists, the communicator (a file-based stand-in for mpi4py) carries the rendezvous."""
+    _launch("gloo", "mpi_comm", 2, timeout=180, extra_env={"FILECOMM_DIR": str(tmp_path)})
+
+
 def test_gloo_mismatched_arguments_raise():
     _launch("gloo", "mismatch", 2)
 
