@@ -242,7 +242,7 @@ class Buffer(LowLatencyMixin):
     def get_combine_config(num_ranks: int) -> Config:
         if num_ranks not in (1, 2, 4, 8):
             raise ValueError(f"unsupported number of EP ranks: {num_ranks}")
-        return Config(Buffer.num_sms, 10 if num_ranks <= 2 else 4, 256, 6, 128)
+        return Config(Buffer.num_sms, {1: 10, 2: 10, 4: 9, 8: 4}[num_ranks], 256, 6, 128)
 
     # ------------------------------------------------------------------ stream protocol helpers
     def _enter(self, previous_event, allocate_on_comm_stream):
